@@ -110,6 +110,10 @@ class ModelConfig:
         """Standard deviation of random matrices in the random-weights mode."""
         return 0.02
 
+    def output_softcap(self) -> float | None:
+        """c when the logits leave the head as c * tanh(logits / c); None when they leave as they are."""
+        return None
+
 
 def read_config_json(model_dir: str | Path) -> dict:
     path = Path(model_dir) / "config.json"

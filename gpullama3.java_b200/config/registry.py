@@ -42,8 +42,10 @@ def registered_architectures() -> list[str]:
 
 def architecture_of(config_dict: dict) -> Architecture:
     archs = config_dict.get("architectures")
+    if archs is None and isinstance(config_dict.get("architecture"), str):
+        archs = [config_dict["architecture"]]   # some families name their one architecture under this key
     if not isinstance(archs, list) or not archs or not isinstance(archs[0], str):
-        raise ConfigError('config.json needs "architectures": ["<name>"]')
+        raise ConfigError('config.json needs "architectures": ["<name>"] (or "architecture": "<name>")')
     name = archs[0]
     arch = _ARCHITECTURES.get(name)
     if arch is None:

@@ -10,9 +10,16 @@
 //   1  residual add  C[M, N] += acc                      (C is the 32-bit residual stream)
 //   2  gated SiLU    C[M, N/2] = silu(acc[2j]) * acc[2j+1]   (W holds gate and up rows interleaved;
 //                    silu(g) = g / (1 + exp(-g)), inference/InferenceCore.java:163-166)
+//   3  gated GELU    the same with gelu(g) = 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))), the tanh form
 #include "common.cuh"
 
 namespace b200 {
+
+// the gated epilogues: activation of the gate value times the up value
+__device__ __forceinline__ float gated_pair(float gate, float up, int epilogue) {
+    if (epilogue == 3) return 0.5f * gate * (1.0f + tanhf(0.7978845608028654f * (gate + 0.044715f * gate * gate * gate))) * up;
+    return (gate / (1.0f + expf(-gate))) * up;
+}
 
 constexpr int kTileM = 64, kTileN = 64, kTileK = 16, kGemmThreads = 256;
 
@@ -55,13 +62,13 @@ gemm_generic_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ W,
     for (int i = 0; i < 4; ++i) {
         const int m = m0 + ty * 4 + i;
         if (m >= M) continue;
-        if (epilogue == 2) {
+        if (epilogue >= 2) {
 #pragma unroll
             for (int j = 0; j < 4; j += 2) {
                 const int n = n0 + tx * 4 + j;
                 if (n + 1 < N) {
                     const float gate = acc[i][j], up = acc[i][j + 1];
-                    C[(size_t)m * ldc + n / 2] = from_f32<TC>((gate / (1.0f + expf(-gate))) * up);
+                    C[(size_t)m * ldc + n / 2] = from_f32<TC>(gated_pair(gate, up, epilogue));
                 }
             }
         } else {
@@ -129,13 +136,13 @@ gemm_generic_big_kernel(const TA* __restrict__ A, int lda, const TW* __restrict_
     for (int i = 0; i < 8; ++i) {
         const int m = m0 + ty * 8 + i;
         if (m >= M) continue;
-        if (epilogue == 2) {
+        if (epilogue >= 2) {
 #pragma unroll
             for (int j = 0; j < 8; j += 2) {
                 const int n = n0 + tx * 8 + j;
                 if (n + 1 < N) {
                     const float gate = acc[i][j], up = acc[i][j + 1];
-                    C[(size_t)m * ldc + n / 2] = from_f32<TC>((gate / (1.0f + expf(-gate))) * up);
+                    C[(size_t)m * ldc + n / 2] = from_f32<TC>(gated_pair(gate, up, epilogue));
                 }
             }
         } else {
@@ -229,12 +236,12 @@ gemm_fewrows_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ W,
     float sum = 0.f;
 #pragma unroll
     for (int wp = 0; wp < kFewWarps; ++wp) sum += part[wp][i];
-    if (epilogue == 2) {
+    if (epilogue >= 2) {
         float up = 0.f;   // the gate row's thread also adds up the up row (the next row of the CTA)
         if ((r & 1) == 0) {
 #pragma unroll
             for (int wp = 0; wp < kFewWarps; ++wp) up += part[wp][i + MT];
-            if (m < M && n + 1 < N) C[(size_t)m * ldc + n / 2] = from_f32<TC>((sum / (1.0f + expf(-sum))) * up);
+            if (m < M && n + 1 < N) C[(size_t)m * ldc + n / 2] = from_f32<TC>(gated_pair(sum, up, epilogue));
         }
     } else if (m < M && n < N) {
         TC* c = C + (size_t)m * ldc + n;
@@ -259,9 +266,9 @@ static int launch_fewrows(const void* A, int lda, const void* W, int ldw, void* 
 extern "C" int b200_gemm_generic(const void* A, int a_dtype, int lda, const void* W, int w_dtype, int ldw, void* C,
                                  int c_dtype, int ldc, int M, int N, int K, int epilogue, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
-    if (K <= 0 || epilogue < 0 || epilogue > 2) return b200::kErrBadArgument;
+    if (K <= 0 || epilogue < 0 || epilogue > 3) return b200::kErrBadArgument;
     if (epilogue == 1 && c_dtype != b200::kF32) return b200::kErrBadArgument;
-    if (epilogue == 2 && (N & 1)) return b200::kErrBadArgument;
+    if (epilogue >= 2 && (N & 1)) return b200::kErrBadArgument;
     // a decode step's few rows: rows of 4 elements at a time, when the rows start on such a boundary
     const size_t a_el = a_dtype == b200::kF32 ? 4 : 2, w_el = w_dtype == b200::kF32 ? 4 : 2;
     if (M <= 16 && K % 4 == 0 && lda % 4 == 0 && ldw % 4 == 0 && ((uintptr_t)A % (4 * a_el)) == 0 && ((uintptr_t)W % (4 * w_el)) == 0) {

@@ -1,0 +1,98 @@
+// What happens to the rows of a projection between the product and the attention kernels, for mixers whose
+// queries, keys, values or latents are not used as the product leaves them:
+//     z = x[src + r d .. + d] (+ bias)              one row of d numbers per (token, head)
+//     z <- z / sqrt(mean(z^2) + eps)                (optional: an RMS norm per row, 32-bit)
+//     z <- z * weight[0 .. d)                       (optional: the norm's weight, shared by the rows)
+//     z <- z * mul                                  (a score scale folded into the queries, or 1)
+//     dst[dst_off + r d_pad .. + d_pad] = z, 0, ..., 0   (rows may be widened with zeros to the size a kernel takes)
+// Up to four such segments of a token's row are handled by one launch (queries, keys and values of an attention
+// layer; a latent that is stored once as keys and once as values).  A warp per (token, row).
+#include "common.cuh"
+
+namespace b200 {
+
+constexpr int kRowSegments = 4;
+constexpr int kRowThreads = 128;
+
+struct RowSegment {
+    int src_off, n_rows, d, dst_off, d_pad;
+    int bias_off;     // into `bias`, -1: none
+    int norm;         // 1: divide by the row's root mean square
+    int weight_off;   // into `weight`, -1: none
+    float mul;
+};
+struct RowSegments {
+    RowSegment seg[kRowSegments];
+    int n;
+    int total_rows;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(kRowThreads)
+head_rows_kernel(const T* __restrict__ src, int ld_src, T* __restrict__ dst, int ld_dst, const float* __restrict__ bias,
+                 const float* __restrict__ weight, RowSegments segs, float eps) {
+    const int t = blockIdx.x, lane = threadIdx.x & 31;
+    int row = blockIdx.y * (kRowThreads / 32) + (threadIdx.x >> 5);
+    if (row >= segs.total_rows) return;
+    int s = 0;
+    while (s + 1 < segs.n && row >= segs.seg[s].n_rows) {
+        row -= segs.seg[s].n_rows;
+        ++s;
+    }
+    const RowSegment g = segs.seg[s];
+    const T* x = src + (size_t)t * ld_src + g.src_off + (size_t)row * g.d;
+    const float* b = g.bias_off >= 0 ? bias + g.bias_off + (size_t)row * g.d : nullptr;
+    float factor = g.mul;
+    if (g.norm) {
+        float ss = 0.f;
+        for (int e = lane; e < g.d; e += 32) {
+            const float z = to_f32<T>(x[e]) + (b ? b[e] : 0.f);
+            ss += z * z;
+        }
+        ss = warp_sum(ss);
+        factor *= 1.0f / sqrtf(ss / (float)g.d + eps);
+    }
+    const float* w = g.weight_off >= 0 ? weight + g.weight_off : nullptr;
+    T* o = dst + (size_t)t * ld_dst + g.dst_off + (size_t)row * g.d_pad;
+    for (int e = lane; e < g.d_pad; e += 32) {
+        float z = 0.f;
+        if (e < g.d) {
+            z = (to_f32<T>(x[e]) + (b ? b[e] : 0.f)) * factor;
+            if (w) z *= w[e];
+        }
+        o[e] = from_f32<T>(z);
+    }
+}
+
+}  // namespace b200
+
+// `segments`: n_segments records of nine 32-bit words each (src_off, n_rows, d, dst_off, d_pad, bias_off, norm,
+// weight_off, mul as float bits), read on the host.
+extern "C" int b200_head_rows(const void* src, int ld_src, void* dst, int ld_dst, int dtype, const float* bias,
+                              const float* weight, const int* segments, int n_segments, int n_tokens, float eps,
+                              cudaStream_t stream) {
+    if (n_tokens <= 0 || n_segments <= 0) return 0;
+    if (n_segments > b200::kRowSegments) return b200::kErrBadArgument;
+    b200::RowSegments segs = {};
+    segs.n = n_segments;
+    for (int i = 0; i < n_segments; ++i) {
+        const int* p = segments + 9 * i;
+        b200::RowSegment& g = segs.seg[i];
+        g.src_off = p[0]; g.n_rows = p[1]; g.d = p[2]; g.dst_off = p[3]; g.d_pad = p[4];
+        g.bias_off = p[5]; g.norm = p[6]; g.weight_off = p[7];
+        union { int i; float f; } u;
+        u.i = p[8];
+        g.mul = u.f;
+        if (g.n_rows < 0 || g.d < 1 || g.d_pad < g.d) return b200::kErrBadArgument;
+        if ((g.bias_off >= 0 && bias == nullptr) || (g.weight_off >= 0 && weight == nullptr)) return b200::kErrBadArgument;
+        segs.total_rows += g.n_rows;
+    }
+    if (segs.total_rows == 0) return 0;
+    const int per_cta = b200::kRowThreads / 32;
+    dim3 grid(n_tokens, (segs.total_rows + per_cta - 1) / per_cta);
+    if (grid.y > 65535) return b200::kErrUnsupportedSize;
+    B200_DISPATCH_DTYPE(dtype, T,
+        b200::head_rows_kernel<T><<<grid, b200::kRowThreads, 0, stream>>>((const T*)src, ld_src, (T*)dst, ld_dst, bias,
+                                                                          weight, segs, eps));
+    return b200::launch_status();
+}

@@ -15,6 +15,7 @@ from ..cache.sequence_cache import SequenceCache
 from ..config.base import ConfigError, ModelConfig, ScheduleEntry
 from ..parts.base import Block, Part, StepContext, all_parts, build_block, build_part
 from ..parts.embedding import OutputHead, TokenEmbedding
+from ..parts.streams import close_streams_norm, open_streams
 from ..weights.loader import ParamSpec, load_checkpoint_tensors
 from ..weights.safetensors_io import WeightError
 
@@ -28,7 +29,13 @@ class CausalLM:
         self.blocks: list[Block] = [build_block(s) for s in config.layer_specs()]
         self.final_norm = build_part(config.final_norm())
         self.head = OutputHead(config.vocab_size, config.hidden_size,
-                               tied_to=self.embedding if config.tie_word_embeddings else None)
+                               tied_to=self.embedding if config.tie_word_embeddings else None,
+                               softcap=config.output_softcap())
+        # blocks that keep several residual streams per token say how many; all blocks of a model agree
+        counts = {getattr(b, "streams", None) for b in self.blocks}
+        if len(counts) > 1:
+            raise ConfigError(f"the blocks of a model must agree on the residual streams, got {sorted(map(str, counts))}")
+        self.streams: int | None = counts.pop() if counts else None
         self.schedule: list[ScheduleEntry] = list(config.schedule())
         self._check_schedule()
         self.loaded = False
@@ -142,6 +149,8 @@ class CausalLM:
             raise WeightError("the model has no weights yet (load_folder / load_random / load_tensors)")
         ws = ctx.workspace
         residual = self.embedding.forward(ctx.tokens, ctx.empty)  # float32 [T, hidden]; lives for the whole pass
+        if self.streams is not None:
+            residual = open_streams(residual, self.streams, ctx.empty)   # [T, streams, hidden]
         # a block may leave the first norm of the block that runs next to that block's first product
         # (parts/base.py, ScaledRows); blocks that do not offer this are called the plain way
         handed = None
@@ -160,7 +169,10 @@ class CausalLM:
                 ws.release(mark)   # the block's intermediate tensors; what it hands on does not come from there
         if logit_rows is None or logit_rows.numel() == 0:
             return None
-        x = self.final_norm.forward(residual, ctx.dtype, rows=logit_rows, alloc=ctx.empty)
+        if self.streams is not None:
+            x = close_streams_norm(residual, self.final_norm, ctx.dtype, logit_rows, ctx.empty)
+        else:
+            x = self.final_norm.forward(residual, ctx.dtype, rows=logit_rows, alloc=ctx.empty)
         return self.head.forward(x)
 
 

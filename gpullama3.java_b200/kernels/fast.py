@@ -11,8 +11,16 @@ import torch
 from . import ops
 
 
+def gemm_has_epilogue(a, w: torch.Tensor, epilogue: int) -> bool:
+    """Whether the kernel that will multiply ``a`` with ``w`` applies ``epilogue`` itself.  The plain kernel has all
+    of them; the tensor-core kernels of the bfloat16 run have the store, the residual sum and the gated SiLU."""
+    if getattr(a, "dtype", None) != torch.bfloat16 or w.dtype != torch.bfloat16:
+        return True
+    return epilogue != ops.EPILOGUE_GATED_GELU_TANH
+
+
 def try_gemm(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int) -> bool:
-    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or epilogue == ops.EPILOGUE_GATED_GELU_TANH:
         return False
     M = a.shape[0]
     if M <= 16:

@@ -68,6 +68,20 @@ _SIGNATURES = {
                                                                 c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
                                                                 c_int, c_int, c_int, c_int]),
     "b200_random_fill": ("random_init", [c_void_p, c_int, ctypes.c_longlong, ctypes.c_ulonglong, c_float, c_float]),
+    "b200_streams_combine": ("streams", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int]),
+    "b200_streams_read_norm": ("streams", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
+                                           c_float]),
+    "b200_head_rows": ("head_rows", [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                     c_float]),
+    "b200_softcap_rows": ("elementwise", [c_void_p, ctypes.c_longlong, c_float]),
+    "b200_gated_activation": ("elementwise", [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int]),
+    "b200_gated_rmsnorm": ("elementwise", [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
+                                           c_float]),
+    "b200_causal_conv_silu": ("delta_rule", [c_void_p, c_int, c_void_p, c_void_p, ctypes.c_longlong, c_void_p, c_void_p,
+                                             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int]),
+    "b200_delta_rule_scan": ("delta_rule", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                                            ctypes.c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                            c_int, c_int, c_float, c_float]),
     "b200_argmax_rows": ("sampling", [c_void_p, c_int, c_void_p, c_int, c_int]),
     "b200_sample_rows": ("sampling", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_void_p]),
 }
@@ -245,17 +259,19 @@ def attention_paged(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, posit
 
 
 # --------------------------------------------------------------------------- matrix products
-EPILOGUE_STORE, EPILOGUE_RESIDUAL_ADD, EPILOGUE_GATED_SILU = 0, 1, 2
+EPILOGUE_STORE, EPILOGUE_RESIDUAL_ADD, EPILOGUE_GATED_SILU, EPILOGUE_GATED_GELU_TANH = 0, 1, 2, 3
+GATED_EPILOGUES = (EPILOGUE_GATED_SILU, EPILOGUE_GATED_GELU_TANH)
+ACTIVATION_CODES = {"silu": 0, "gelu_tanh": 1}   # elementwise.cu
 
 
 def gemm_generic(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int = EPILOGUE_STORE) -> None:
-    """c = a @ w.T (store), c += a @ w.T (residual add, c float32) or c = silu(gate) * up with
-    gate/up rows interleaved in w.  32-bit FMA accumulation, no tensor cores."""
+    """c = a @ w.T (store), c += a @ w.T (residual add, c float32) or c = act(gate) * up with
+    gate/up rows interleaved in w (act: SiLU, or GELU in its tanh form).  32-bit FMA accumulation, no tensor cores."""
     _dev(a, w, c)
     M, K = a.shape
     N = w.shape[0]
     assert w.shape[1] == K and a.stride(1) == 1 and w.stride(1) == 1 and c.stride(1) == 1
-    assert c.shape[0] == M and c.shape[1] == (N // 2 if epilogue == EPILOGUE_GATED_SILU else N)
+    assert c.shape[0] == M and c.shape[1] == (N // 2 if epilogue in GATED_EPILOGUES else N)
     _check(_fn("b200_gemm_generic")(
         a.data_ptr(), dtype_code(a.dtype), a.stride(0), w.data_ptr(), dtype_code(w.dtype), w.stride(0), c.data_ptr(),
         dtype_code(c.dtype), c.stride(0), M, N, K, epilogue, _stream()), "gemm_generic")
@@ -619,3 +635,146 @@ def sample_rows(logits: torch.Tensor, uniforms: torch.Tensor, out: torch.Tensor,
                                    logits.shape[0], logits.shape[1], float(temperature), float(top_p),
                                    scratch.data_ptr() if scratch is not None else None, _stream()),
            "sample_rows")
+
+
+# --------------------------------------------------------------------------- several residual streams
+MAX_STREAMS = 8   # streams.cu
+
+
+def streams_combine(x: torch.Tensor, out: torch.Tensor, mix: torch.Tensor, write: torch.Tensor | None = None,
+                    y: torch.Tensor | None = None) -> None:
+    """out[t, j] = sum_a mix[a, j] x[t, a] (+ write[j] y[t]) over float32 streams x [T, S_in, width] -> out
+    [T, S_out, width]; ``out`` may be ``x`` when S_in == S_out."""
+    _dev(x, out, mix, write, y)
+    T, s_in, width = x.shape
+    s_out = out.shape[1]
+    assert x.dtype == out.dtype == mix.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous()
+    assert out.shape[0] == T and out.shape[2] == width and mix.is_contiguous() and mix.numel() == s_in * s_out
+    if y is not None:
+        assert write is not None and write.dtype == y.dtype == torch.float32 and write.numel() == s_out
+        assert y.is_contiguous() and tuple(y.shape) == (T, width)
+    _check(_fn("b200_streams_combine")(x.data_ptr(), out.data_ptr(), mix.data_ptr(),
+                                       write.data_ptr() if y is not None else None, y.data_ptr() if y is not None else None,
+                                       T, s_in, s_out, width, _stream()), "streams_combine")
+
+
+def streams_read_norm(x: torch.Tensor, read: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float,
+                      rows: torch.Tensor | None = None) -> None:
+    """out[r] = weight * u / sqrt(mean(u^2) + eps), u = sum_a read[a] x[rows[r], a]: x float32 [T, S, width]."""
+    _dev(x, read, weight, out, rows)
+    T, s, width = x.shape
+    assert x.dtype == read.dtype == weight.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous()
+    assert read.numel() == s and weight.numel() == width and out.shape[1] == width
+    n_rows = out.shape[0]
+    if rows is not None:
+        assert rows.dtype == torch.int32 and rows.numel() == n_rows
+    else:
+        assert n_rows == T
+    _check(_fn("b200_streams_read_norm")(x.data_ptr(), read.data_ptr(), weight.data_ptr(), out.data_ptr(),
+                                         dtype_code(out.dtype), rows.data_ptr() if rows is not None else None, n_rows, s,
+                                         width, float(eps), _stream()), "streams_read_norm")
+
+
+# --------------------------------------------------------------------------- rows of a projection, per head
+def head_row_segment(src_off: int, n_rows: int, d: int, dst_off: int, d_pad: int | None = None, bias_off: int = -1,
+                     norm: bool = False, weight_off: int = -1, mul: float = 1.0) -> list[int]:
+    """One segment of ``head_rows``: ``n_rows`` rows of ``d`` numbers from column ``src_off`` on, each (+ bias)
+    (normalised) (* weight) * mul, written ``d_pad`` wide (zeros behind the ``d``) from column ``dst_off`` on."""
+    import struct
+
+    return [src_off, n_rows, d, dst_off, d if d_pad is None else d_pad, bias_off, 1 if norm else 0, weight_off,
+            struct.unpack("<i", struct.pack("<f", float(mul)))[0]]
+
+
+def head_rows(src: torch.Tensor, dst: torch.Tensor, segments, eps: float = 0.0, bias: torch.Tensor | None = None,
+              weight: torch.Tensor | None = None) -> None:
+    """``segments``: a ctypes array made by ``head_row_segments`` (at most four segments)."""
+    _dev(src, dst, bias, weight)
+    assert src.dtype == dst.dtype and src.stride(1) == 1 and dst.stride(1) == 1 and src.shape[0] == dst.shape[0]
+    assert bias is None or (bias.dtype == torch.float32 and bias.is_contiguous())
+    assert weight is None or (weight.dtype == torch.float32 and weight.is_contiguous())
+    _check(_fn("b200_head_rows")(src.data_ptr(), src.stride(0), dst.data_ptr(), dst.stride(0), dtype_code(src.dtype),
+                                 bias.data_ptr() if bias is not None else None,
+                                 weight.data_ptr() if weight is not None else None, ctypes.addressof(segments),
+                                 len(segments) // 9, src.shape[0], float(eps), _stream()), "head_rows")
+
+
+def head_row_segments(*segments: list[int]):
+    """The segments of one ``head_rows`` launch as the C function reads them (kept by the part that made them)."""
+    flat = [v for s in segments for v in s]
+    return (ctypes.c_int * len(flat))(*flat)
+
+
+# --------------------------------------------------------------------------- small per-element kernels
+def softcap_rows(logits: torch.Tensor, cap: float) -> None:
+    """logits <- cap * tanh(logits / cap), in place (float32)."""
+    _dev(logits)
+    assert logits.dtype == torch.float32 and logits.is_contiguous()
+    _check(_fn("b200_softcap_rows")(logits.data_ptr(), logits.numel(), float(cap), _stream()), "softcap_rows")
+
+
+def gated_activation(pairs: torch.Tensor, out: torch.Tensor, activation: int) -> None:
+    """out[t, j] = act(pairs[t, 2j]) * pairs[t, 2j + 1]."""
+    _dev(pairs, out)
+    assert pairs.dtype == out.dtype and pairs.stride(1) == 1 and out.stride(1) == 1
+    assert pairs.shape[0] == out.shape[0] and pairs.shape[1] == 2 * out.shape[1]
+    _check(_fn("b200_gated_activation")(pairs.data_ptr(), pairs.stride(0), out.data_ptr(), out.stride(0),
+                                        dtype_code(out.dtype), out.shape[0], out.shape[1], int(activation), _stream()),
+           "gated_activation")
+
+
+def gated_rmsnorm(x: torch.Tensor, weight: torch.Tensor, gate: torch.Tensor, out: torch.Tensor, n_heads: int, d: int,
+                  eps: float) -> None:
+    """Per (token, head) row of float32 x [T, n_heads d]: x / sqrt(mean(x^2) + eps) * weight[d] * sigmoid(gate)."""
+    _dev(x, weight, gate, out)
+    assert x.dtype == weight.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous() and gate.stride(1) == 1
+    assert x.shape[1] == n_heads * d == out.shape[1] and gate.shape[1] >= n_heads * d and weight.numel() == d
+    assert gate.dtype == out.dtype
+    _check(_fn("b200_gated_rmsnorm")(x.data_ptr(), weight.data_ptr(), gate.data_ptr(), gate.stride(0), out.data_ptr(),
+                                     dtype_code(out.dtype), x.shape[0], n_heads, d, float(eps), _stream()), "gated_rmsnorm")
+
+
+# --------------------------------------------------------------------------- short convolution and the delta rule
+MAX_CONV_TAPS = 16   # delta_rule.cu
+
+
+def causal_conv_silu(x: torch.Tensor, weight: torch.Tensor, state: torch.Tensor, slots: torch.Tensor,
+                     seq_ids: torch.Tensor, cu_seqlens: torch.Tensor, out: torch.Tensor, channels: int,
+                     update_state: bool = True) -> None:
+    """out[t, c] = silu(sum_j weight[c, j] x[t - (taps - 1) + j, c]) per sequence of the packed step; inputs before
+    the step come from ``state`` [slots, >= (taps - 1) * channels] (float32, oldest first), which then takes the
+    step's last taps - 1 inputs.  x [T, >= channels]."""
+    _dev(x, weight, state, slots, seq_ids, cu_seqlens, out)
+    taps = weight.shape[1]
+    assert weight.dtype == state.dtype == torch.float32 and weight.is_contiguous() and weight.shape[0] == channels
+    assert x.dtype == out.dtype and x.stride(1) == 1 and out.stride(1) == 1 and state.stride(1) == 1
+    assert state.shape[1] >= (taps - 1) * channels
+    _check(_fn("b200_causal_conv_silu")(x.data_ptr(), x.stride(0), weight.data_ptr(), state.data_ptr(), state.stride(0),
+                                        slots.data_ptr(), seq_ids.data_ptr(), cu_seqlens.data_ptr(), out.data_ptr(),
+                                        out.stride(0), dtype_code(x.dtype), x.shape[0], slots.numel(), channels, taps,
+                                        1 if update_state else 0, _stream()), "causal_conv_silu")
+
+
+def delta_rule_supported(d_k: int) -> bool:
+    lib = library("delta_rule")
+    a, b = c_int(0), c_int(0)
+    return bool(lib.b200_delta_rule_plan(c_int(d_k), ctypes.byref(a), ctypes.byref(b)))
+
+
+def delta_rule_scan(qkv: torch.Tensor, beta: torch.Tensor, decay: torch.Tensor, dt_bias: torch.Tensor,
+                    a_log: torch.Tensor, state: torch.Tensor, slots: torch.Tensor, cu_seqlens: torch.Tensor,
+                    out: torch.Tensor, heads: int, kv_heads: int, d_k: int, d_v: int, q_scale: float,
+                    unit_eps: float) -> None:
+    """The gated delta rule over a packed step.  qkv [T, 2 kv_heads d_k + heads d_v] (after the convolution), beta
+    [T, >= heads] and decay [T, >= heads d_k] as the projections leave them, state float32 [slots, >= heads d_k d_v]
+    (updated in place), out float32 [T, heads d_v]."""
+    _dev(qkv, beta, decay, dt_bias, a_log, state, slots, cu_seqlens, out)
+    assert qkv.dtype == beta.dtype == decay.dtype and qkv.stride(1) == beta.stride(1) == decay.stride(1) == 1
+    assert dt_bias.dtype == a_log.dtype == state.dtype == out.dtype == torch.float32 and out.is_contiguous()
+    assert dt_bias.numel() == heads * d_k and a_log.numel() == heads and state.stride(1) == 1
+    assert state.shape[1] >= heads * d_k * d_v and out.shape[1] == heads * d_v and out.shape[0] == qkv.shape[0]
+    _check(_fn("b200_delta_rule_scan")(qkv.data_ptr(), qkv.stride(0), beta.data_ptr(), beta.stride(0), decay.data_ptr(),
+                                       decay.stride(0), dt_bias.data_ptr(), a_log.data_ptr(), state.data_ptr(),
+                                       state.stride(0), slots.data_ptr(), cu_seqlens.data_ptr(), out.data_ptr(),
+                                       dtype_code(qkv.dtype), slots.numel(), heads, kv_heads, d_k, d_v, float(q_scale),
+                                       float(unit_eps), _stream()), "delta_rule_scan")

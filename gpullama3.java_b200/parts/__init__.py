@@ -9,9 +9,13 @@ from .attention import GroupedQueryAttention
 from .feed_forward import SwiGLUFeedForward
 from .block import PreNormBlock
 from .embedding import OutputHead, TokenEmbedding
+from .streams import ConnectedBlock, StreamConnection
+from .latent_attention import LatentAttention
+from .delta_rule import ChannelDeltaRule
 
 __all__ = ["Block", "FeedForward", "Mixer", "Norm", "Part", "PartRegistryError", "PositionEncoding", "ScaledRows",
            "StepContext", "all_parts", "build_block", "build_part", "register_block", "register_feed_forward",
            "register_mixer", "register_norm", "register_part", "register_position_encoding", "registered", "unregister", "Linear", "RMSNorm", "NoPositionEncoding",
            "RotaryPositionEncoding", "llama3_inverse_frequencies", "GroupedQueryAttention", "SwiGLUFeedForward",
-           "PreNormBlock", "OutputHead", "TokenEmbedding"]
+           "PreNormBlock", "OutputHead", "TokenEmbedding", "ConnectedBlock", "StreamConnection", "LatentAttention",
+           "ChannelDeltaRule"]

@@ -40,8 +40,11 @@ class OutputHead(Part):
     graph_safe = True
     pad_safe = True
 
-    def __init__(self, vocab_size: int, hidden_size: int, tied_to: TokenEmbedding | None = None):
+    def __init__(self, vocab_size: int, hidden_size: int, tied_to: TokenEmbedding | None = None,
+                 softcap: float | None = None):
+        """``softcap`` c: logits leave as c * tanh(logits / c)."""
         self.vocab_size, self.hidden_size, self.tied_to = vocab_size, hidden_size, tied_to
+        self.softcap = float(softcap) if softcap else None
         self.linear: Linear | None = None
 
     def parameters(self):
@@ -56,4 +59,7 @@ class OutputHead(Part):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         """x: normalised rows [R, hidden] -> float32 logits [R, vocab]."""
-        return self.linear.store(x, torch.float32)
+        logits = self.linear.store(x, torch.float32)
+        if self.softcap is not None:
+            ops.softcap_rows(logits, self.softcap)
+        return logits

@@ -7,6 +7,8 @@ from __future__ import annotations
 
 import torch
 
+from ..config.base import ConfigError
+from ..kernels import ops
 from ..weights.loader import ParamSpec
 from .base import FeedForward, StepContext, register_feed_forward
 from .linear import Linear
@@ -16,8 +18,11 @@ class SwiGLUFeedForward(FeedForward):
     graph_safe = True
     pad_safe = True
 
-    def __init__(self, hidden_size: int, intermediate_size: int):
-        self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
+    def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "silu"):
+        """``activation`` of the gate: ``silu`` (SwiGLU) or ``gelu_tanh`` (GELU in its tanh form)."""
+        if activation not in ops.ACTIVATION_CODES:
+            raise ConfigError(f"feed-forward activation {activation!r}; known: {', '.join(sorted(ops.ACTIVATION_CODES))}")
+        self.hidden_size, self.intermediate_size, self.activation = hidden_size, intermediate_size, activation
         self.gate_up: Linear | None = None
         self.down: Linear | None = None
 
@@ -34,11 +39,12 @@ class SwiGLUFeedForward(FeedForward):
         self.down = Linear(down.to(torch.float32 if dtype == torch.float32 else down.dtype).contiguous())
 
     def takes_scaled_rows(self, ctx: StepContext) -> bool:
-        return ctx.all_decode and self.gate_up.links_with(ctx.n_tokens, ctx.dtype)
+        return ctx.all_decode and self.activation == "silu" and self.gate_up.links_with(ctx.n_tokens, ctx.dtype)
 
     def forward(self, x, ctx: StepContext, residual, then_norm=None):
-        h = self.gate_up.gated_silu(x, ctx.dtype, ctx.empty)  # [T, intermediate]
+        h = self.gate_up.gated(x, ctx.dtype, ctx.empty, self.activation)  # [T, intermediate]
         return self.down.add_to(h, residual, then_norm)
 
 
 register_feed_forward("swiglu", SwiGLUFeedForward)
+register_feed_forward("gated", SwiGLUFeedForward)   # the same arrangement, the gate's activation named by the configuration

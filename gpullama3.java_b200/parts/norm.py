@@ -13,18 +13,22 @@ class RMSNorm(Norm):
     graph_safe = True
     pad_safe = True
 
-    def __init__(self, dim: int, eps: float):
-        self.dim, self.eps = int(dim), float(eps)
+    def __init__(self, dim: int, eps: float, offset: float = 0.0):
+        """``offset``: what is added to the stored weight (1.0 for a weight that is stored around zero and applied
+        as 1 + w); the sum is formed once at load, in 32 bits, and the weight is then kept in 32 bits."""
+        self.dim, self.eps, self.offset = int(dim), float(eps), float(offset)
         self.weight: torch.Tensor | None = None
 
     def parameters(self):
-        return {"weight": ParamSpec((self.dim,), "norm")}
+        return {"weight": ParamSpec((self.dim,), "norm" if self.offset == 0.0 else "matrix")}
 
     def load(self, tensors, dtype, device):
         w = tensors["weight"]
         # a weight stored in 32 bits stays so; the float32 run takes everything in 32 bits
-        keep = torch.float32 if (dtype == torch.float32 or w.dtype == torch.float32) else torch.bfloat16
+        keep = torch.float32 if (dtype == torch.float32 or w.dtype == torch.float32 or self.offset != 0.0) else torch.bfloat16
         self.weight = w.to(device=device, dtype=keep).contiguous()
+        if self.offset != 0.0:
+            self.weight += self.offset
 
     def row_factor_form(self):
         return self.weight, self.eps, self.dim

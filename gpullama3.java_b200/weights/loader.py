@@ -23,9 +23,13 @@ from .safetensors_io import WeightError, open_model_files
 @dataclass(frozen=True)
 class ParamSpec:
     """One parameter of a part: its shape and how the random-weights mode fills it
-    (``matrix``: N(0, std); ``norm``: 1 + N(0, norm_std); ``zeros``; ``int_table``)."""
+    (``matrix``: N(0, std); ``norm``: 1 + N(0, norm_std); ``zeros``; ``int_table``; ``normal``: N(mean, std) with
+    the two numbers given here).  A dimension of -1 is read from the checkpoint (a rank that no configuration key
+    gives); such a parameter cannot be filled at random."""
     shape: tuple[int, ...]
     init: str = "matrix"
+    mean: float = 0.0
+    std: float = 0.0
 
 
 def storage_dtype(stored: torch.dtype, run_dtype: torch.dtype) -> torch.dtype:
@@ -43,7 +47,10 @@ def check_names_and_shapes(expected: dict[str, tuple[int, ...]], found: dict[str
     """Raise one WeightError that lists everything wrong; ``optional`` names may be present or not."""
     missing = sorted(n for n in expected if n not in found)
     unexpected = sorted(n for n in found if n not in expected and n not in optional)
-    wrong = sorted((n, found[n], expected[n]) for n in expected if n in found and tuple(found[n]) != tuple(expected[n]))
+    def fits(f, e):
+        return len(f) == len(e) and all(b == -1 or a == b for a, b in zip(f, e))
+
+    wrong = sorted((n, found[n], expected[n]) for n in expected if n in found and not fits(tuple(found[n]), tuple(expected[n])))
     if not (missing or unexpected or wrong):
         return
     lines = [f"weights in {where} do not match the model:"]

@@ -77,8 +77,12 @@ def random_tensor(name: str, spec: ParamSpec, seed: int, std: float, norm_std: f
         return torch.zeros(spec.shape, device=device, dtype=torch.int32)
     if spec.init == "zeros" or (spec.init == "norm" and not norm_std):
         return torch.full(spec.shape, 0.0 if spec.init == "zeros" else 1.0, device=device, dtype=dtype)
+    if any(d < 0 for d in spec.shape):
+        raise ValueError(f"{name}: a dimension that only a checkpoint gives cannot be filled at random")
     if spec.init == "matrix":
         s, offset = std, 0.0
+    elif spec.init == "normal":
+        s, offset = spec.std, spec.mean
     elif spec.init == "norm":
         s, offset = norm_std, 1.0
     else:

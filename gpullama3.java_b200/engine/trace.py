@@ -23,6 +23,7 @@ from ..config.base import read_config_json
 from .step import SequenceInput, StepFunction
 
 DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
+SPARE_PAGES = 64   # what the program adds to --max-tokens: a page per request that may be live at once
 
 
 class TraceError(ValueError):
@@ -79,7 +80,7 @@ def main(argv=None) -> int:
     ap.add_argument("--dtype", required=True, choices=sorted(DTYPES))
     ap.add_argument("--out", required=True, help="folder that receives <step>.f32")
     ap.add_argument("--max-tokens", type=int, required=True,
-                    help="most tokens live requests hold at any time, each rounded up to a multiple of 64")
+                    help="most tokens live requests hold at any time")
     args = ap.parse_args(argv)
     if not torch.cuda.is_available():
         print("trace_run: no CUDA device; the engine has no CPU path", file=sys.stderr)
@@ -87,7 +88,8 @@ def main(argv=None) -> int:
     torch.backends.cuda.matmul.allow_tf32 = False
     torch.backends.cudnn.allow_tf32 = False
     model = load_model(args.model, DTYPES[args.dtype], "cuda")
-    runner = TraceRunner(model, args.max_tokens, args.out)
+    # the promise counts tokens, the cache hands out whole pages: room for the partly filled last page of many requests
+    runner = TraceRunner(model, args.max_tokens + SPARE_PAGES * PAGE_TOKENS, args.out)
     for line in sys.stdin:
         line = line.strip()
         if not line:

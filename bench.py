@@ -376,6 +376,135 @@ def run_1b_f32(peaks, layers, warmup, context, batch):
     return {"layers": cfg["num_hidden_layers"], "layers_full": full, "prefill": pre, "decode": dec}
 
 
+# ---------------------------------------------------------------------------------------------------------------
+# --design guduzen: the Guduzen decoder beside a Llama 3 decoder of the same width, depth, heads and vocabulary.
+
+DESIGN_SIZES = {
+    # width, feed-forward, heads / kv heads of size 64 (the delta and latent layers use the same head count), layers
+    "s": dict(width=1024, ff=4096, heads=16, kv_heads=4, dim=64, layers=8, vocab=32768, window=1024, kv_rank=128, q_rank=384),
+    "m": dict(width=2048, ff=8192, heads=32, kv_heads=8, dim=64, layers=16, vocab=128256, window=1024, kv_rank=256, q_rank=768),
+}
+
+
+def guduzen_config(z):
+    """Layers in the order window attention, attention reading its cache, latent attention, delta rule, repeated."""
+    att = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"], "scale": z["dim"] ** -0.5,
+           "mask": {"size": z["window"]}}
+    lat = {"heads": z["heads"], "dim": z["dim"], "vdim": z["dim"], "kv_rank": z["kv_rank"], "q_rank": z["q_rank"],
+           "scale": z["dim"] ** -0.5}
+    delta = {"heads": z["heads"], "kv_heads": z["heads"], "dim": z["dim"], "vdim": z["dim"], "conv": 4, "a_rank": 64, "g_rank": 64}
+    mlp = {"kind": "dense", "ff": z["ff"]}
+    layers = []
+    for i in range(z["layers"]):
+        k = i % 4
+        if k == 0:
+            layers.append({"type": "attention", "mixer": dict(att), "mlp": mlp})
+        elif k == 1:
+            layers.append({"type": "attention", "mixer": dict(att, kv_from=i - 1), "mlp": mlp})
+        elif k == 2:
+            layers.append({"type": "latent_attention", "mixer": dict(lat), "mlp": mlp})
+        else:
+            layers.append({"type": "channel_delta", "mixer": dict(delta), "mlp": mlp})
+    return {"architecture": "Guduzen", "vocab": z["vocab"], "width": z["width"], "streams": 3, "logit_softcap": 30.0,
+            "norm": {"eps": 1e-6}, "layers": layers}
+
+
+def llama_like(z):
+    return {"architectures": ["LlamaForCausalLM"], "num_hidden_layers": z["layers"], "hidden_size": z["width"],
+            "num_attention_heads": z["heads"], "num_key_value_heads": z["kv_heads"], "head_dim": z["dim"],
+            "intermediate_size": z["ff"], "vocab_size": z["vocab"], "rope_theta": 500000.0, "rms_norm_eps": 1e-5,
+            "tie_word_embeddings": True, "max_position_embeddings": 131072}
+
+
+def kernel_table(engine, inputs_fn, graphs: bool):
+    """Device time per kernel function over one step issued launch by launch (recorded steps are not seen)."""
+    from gpullama3.java_b200.kernels import ops
+
+    was = engine.step_fn.use_graphs, engine.step_fn.use_prompt_graphs
+    engine.step_fn.use_graphs = engine.step_fn.use_prompt_graphs = False
+    try:
+        engine.step_fn(inputs_fn())          # warm-up of exactly this step
+        ops.profile_start()
+        engine.step_fn(inputs_fn())
+        table = ops.profile_stop()
+    finally:
+        engine.step_fn.use_graphs, engine.step_fn.use_prompt_graphs = was
+    return {k: [n, round(ms * 1e3, 1)] for k, (n, ms) in sorted(table.items(), key=lambda kv: -kv[1][1])}
+
+
+def run_design_arm(cfg, name, args, peaks):
+    import torch
+    from gpullama3.java_b200.engine.step import SequenceInput
+
+    batch, context, T = args.batch, min(args.context, 2048), 2048
+    engine = make_engine_any(cfg, batch * (context + 256) + T + 4096, batch)
+    V = engine.config.vocab_size
+    g = torch.Generator().manual_seed(4)
+    try:
+        pre_ms = time_prefill(engine, [T], repeats=3)
+        lengths = [context - args.steps - args.warmup] * batch
+        times, launches, _ = time_decode(engine, lengths, args.steps, args.warmup)
+        ms = sum(times) / len(times)
+
+        def prompt_inputs():
+            for s in engine.cache.live_slots():
+                engine.cache.release(s)
+            slot = engine.cache.acquire()
+            return [SequenceInput(slot, torch.randint(0, V, (T,), generator=g).tolist(), [T - 1])]
+
+        prompt_kernels = kernel_table(engine, prompt_inputs, False)
+        for s in engine.cache.live_slots():
+            engine.cache.release(s)
+        slots = [engine.cache.acquire() for _ in range(batch)]
+        engine.step_fn([SequenceInput(s, torch.randint(0, V, (context - 8,), generator=g).tolist(), []) for s in slots])
+        decode_kernels = kernel_table(engine, lambda: [SequenceInput(s, [1], [0]) for s in slots], False)
+        for s in slots:
+            engine.cache.release(s)
+    finally:
+        drop(engine)
+    rec = {"prefill_tokens": T, "prefill_ms": round(pre_ms, 3), "prefill_tokens_per_s": round(T / pre_ms * 1e3, 1),
+           "decode_batch": batch, "decode_context": context, "decode_ms_per_step": round(ms, 4),
+           "decode_tokens_per_s": round(batch / ms * 1e3, 1), "decode_launches": launches,
+           "prompt_kernels_us": prompt_kernels, "decode_kernels_us": decode_kernels}
+    log(f"{name}: prefill {T} in {pre_ms:.2f} ms ({rec['prefill_tokens_per_s']:.0f} tok/s); decode b{batch} at {context}: "
+        f"{ms:.3f} ms/step ({rec['decode_tokens_per_s']:.0f} tok/s)")
+    return rec
+
+
+def make_engine_any(cfg, max_tokens, max_batch):
+    import torch
+    from gpullama3.java_b200.engine.api import Engine
+
+    engine = Engine.from_random(cfg, seed=0, dtype="bfloat16", max_tokens=max_tokens, max_batch=max_batch, norm_std=0.1)
+    torch.cuda.synchronize()
+    return engine
+
+
+def run_design(args, peaks, peak_source, clocks) -> int:
+    """One line: per size, the Guduzen decoder and the Llama 3 decoder of equal width, depth, heads and vocabulary:
+    prompt and decode throughput and the device time of every kernel function in one prompt pass and one decode step."""
+    t0 = time.time()
+    sizes = {}
+    for key in (args.design_sizes.split(",") if args.design_sizes else sorted(DESIGN_SIZES, reverse=True)):
+        z = DESIGN_SIZES[key]
+        sizes[key] = {"sizes": z, "guduzen": run_design_arm(guduzen_config(z), f"guduzen {key}", args, peaks),
+                      "llama": run_design_arm(llama_like(z), f"llama {key}", args, peaks)}
+    clock_summary = clocks.summary(t0, time.time())
+    clocks.stop()
+    first = sizes[next(iter(sizes))]
+    line = {"metric": "decode tokens/s (Guduzen decoder beside a Llama 3 decoder of equal size)",
+            "value": first["guduzen"]["decode_tokens_per_s"], "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": first["guduzen"]["decode_ms_per_step"], "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic: random weights, uniform random token ids",
+            "config": {"model": "Guduzen, layers window attention / shared-cache attention / latent attention / delta rule",
+                       "global_batch": args.batch, "seq_len": min(args.context, 2048), "parallelism": "single GPU"},
+            "peaks": {**peaks, "source": peak_source}, "sizes": sizes, "gpu_launches": first["guduzen"]["decode_launches"],
+            "clocks": clock_summary, "impl": "ours"}
+    print(json.dumps(line))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -393,6 +522,9 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-prefill", action="store_true", help="--model 3b/8b: skip the timed prompt step (launch lists of decode steps)")
+    ap.add_argument("--design", default=None, choices=["guduzen"],
+                    help="instead of the default workload: this decoder beside a Llama 3 decoder of equal size")
+    ap.add_argument("--design-sizes", default="", help="with --design: which of its sizes (s, m), with commas; default all")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -415,6 +547,8 @@ def main() -> int:
     clocks = ClockSampler()
     clocks.start()
     time.sleep(0.3)
+    if args.design:
+        return run_design(args, peaks, peak_source, clocks)
     if args.model != "1b" or args.dtype != "bfloat16":
         return other_headline(args, peaks, peak_source, clocks, headline_steps)
 

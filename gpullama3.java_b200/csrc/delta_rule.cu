@@ -3,12 +3,15 @@
 // Per sequence and head the mixer keeps a matrix S [d_k, d_v] of 32-bit numbers.  A token with unit-length
 // query q and key k [d_k], value v [d_v], write strength beta and per-channel decay g [d_k] in (0, 1) does
 //     S <- diag(g) S ;  u = beta (v - S^T k) ;  S <- S + k u^T ;  o = S^T q
-// in this order.  Column j of S only ever meets column j of v, u and o, so the columns are independent chains:
-// a thread holds RPT rows of one column in registers, R neighbouring lanes share a column (d_k <= R * RPT, rows
-// beyond d_k are zero and stay zero), and the two dot products of a token are finished by log2(R) exchanges.
-// Tokens are taken in chunks of kChunk: the CTA first prepares the chunk in shared memory (unit norms of q and k
-// from the convolution's output, the query scale, beta = sigmoid(.), g = exp(-exp(A_log) softplus(a + dt_bias)),
-// all 32-bit) and then walks it.  The same kernel serves a prompt, a portion of one and a single decoded token: a
+// in this order (the read-out sees the token's own write).  Column j of S only ever meets column j of v, u and o, so
+// the columns are independent chains:
+// a thread holds RPT rows of one column in registers (rows r, r + R, r + 2 R, ...: the R neighbouring lanes that share a
+// column read neighbouring words of shared memory), d_k <= R * RPT, rows beyond d_k are zero and stay zero, and the two
+// sums over the rows that a token needs are finished by log2(R) exchanges.
+// What the chains read is made first, for all tokens at once, by delta_rule_prepare (unit norms of q and k from the
+// convolution's output, the query scale, beta = sigmoid(.), g = exp(-exp(A_log) softplus(a + dt_bias)), all 32-bit);
+// the scan takes tokens in chunks of kChunk through shared memory, the next chunk on its way (cp.async) while one
+// is walked.  The same kernels serve a prompt, a portion of one and a single decoded token: a
 // sequence's tokens are rows cu_seqlens[i] .. cu_seqlens[i + 1] of the step, its state sits in its cache slot.
 //
 // The convolution: channel c of token t gets sum_j w[c, j] x[t - (taps - 1) + j, c] followed by SiLU, where inputs
@@ -67,7 +70,12 @@ __global__ void conv_state_update_kernel(const T* __restrict__ x, int ld_x, floa
     }
 }
 
-struct ScanArgs {
+// What the scan needs of every token, made by a kernel of its own over all tokens at once (a warp per token and head):
+// one row of 32-bit numbers per (head, token), [q | k | g (each d_pad wide, zeros behind the d_k) | v (d_v) | beta | k . q | fill
+// to a multiple of 4], q and k of unit length (q also scaled), g = exp(-exp(A_log) softplus(a + dt_bias)),
+// beta = sigmoid(.).  Rows of one head lie token after token, so a chunk of a sequence's tokens is one contiguous piece
+// that the scan brings into shared memory as it is.
+struct PrepareArgs {
     const void* qkv;        // [T, ld_qkv]: convolved q [kv_heads d_k], k [kv_heads d_k], v [heads d_v]
     int ld_qkv;
     const void* beta;       // [T, ld_beta], column h: before the sigmoid
@@ -76,115 +84,153 @@ struct ScanArgs {
     int ld_decay;
     const float* dt_bias;   // [heads d_k]
     const float* a_log;     // [heads]
-    float* state;           // per slot: [heads][d_k][d_v]
-    size_t slot_stride;
-    const int* slots;
-    const int* cu_seqlens;
-    float* out;             // [T, heads d_v] 32-bit
-    int heads, kv_heads, d_k, d_v, lanes;   // lanes = R
+    float* rows;            // [heads, T, row]
+    int n_tokens, heads, kv_heads, d_k, d_v, d_pad, row;
     float q_scale, unit_eps;
 };
 
 __device__ __forceinline__ float softplus(float x) { return x > 20.f ? x : log1pf(expf(x)); }
 
-template <typename T, int RPT>
+template <typename T>
+__global__ void __launch_bounds__(128)
+delta_rule_prepare_kernel(PrepareArgs a) {
+    const long long unit = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (unit >= (long long)a.n_tokens * a.heads) return;
+    const size_t t = (size_t)(unit / a.heads);
+    const int h = (int)(unit % a.heads), kvh = h / (a.heads / a.kv_heads);
+    const T* qr = (const T*)a.qkv + t * a.ld_qkv + (size_t)kvh * a.d_k;
+    const T* kr = qr + (size_t)a.kv_heads * a.d_k;
+    const T* vr = (const T*)a.qkv + t * a.ld_qkv + 2 * (size_t)a.kv_heads * a.d_k + (size_t)h * a.d_v;
+    const T* dr = (const T*)a.decay + t * a.ld_decay + (size_t)h * a.d_k;
+    float* out = a.rows + ((size_t)h * a.n_tokens + t) * a.row;
+    float sq = 0.f, sk = 0.f, qk = 0.f;
+    for (int i = lane; i < a.d_k; i += 32) {
+        const float qv = to_f32<T>(qr[i]), kv = to_f32<T>(kr[i]);
+        sq += qv * qv;
+        sk += kv * kv;
+        qk += qv * kv;
+    }
+    sq = warp_sum(sq);
+    sk = warp_sum(sk);
+    qk = warp_sum(qk);
+    const float fq = a.q_scale / sqrtf(sq + a.unit_eps), fk = 1.0f / sqrtf(sk + a.unit_eps);
+    const float neg_rate = -expf(a.a_log[h]);
+    for (int i = lane; i < a.d_pad; i += 32) {
+        const bool in = i < a.d_k;
+        out[i] = in ? to_f32<T>(qr[i]) * fq : 0.f;
+        out[a.d_pad + i] = in ? to_f32<T>(kr[i]) * fk : 0.f;
+        out[2 * a.d_pad + i] = in ? expf(neg_rate * softplus(to_f32<T>(dr[i]) + a.dt_bias[(size_t)h * a.d_k + i])) : 0.f;
+    }
+    for (int j = lane; j < a.d_v; j += 32) out[3 * a.d_pad + j] = to_f32<T>(vr[j]);
+    if (lane == 0) {
+        out[3 * a.d_pad + a.d_v] = 1.0f / (1.0f + expf(-to_f32<T>(((const T*)a.beta)[t * a.ld_beta + h])));
+        out[3 * a.d_pad + a.d_v + 1] = qk * fq * fk;   // k . q of the unit vectors (q scaled)
+    }
+}
+
+struct ScanArgs {
+    const float* rows;      // [heads, T, row] as delta_rule_prepare leaves them
+    float* state;           // per slot: [heads][d_k][d_v]
+    size_t slot_stride;
+    const int* slots;
+    const int* cu_seqlens;
+    float* out;             // [T, heads d_v] 32-bit
+    int n_tokens, heads, d_k, d_v, row;
+};
+
+__device__ __forceinline__ void copy_async_16(float* dst, const float* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void copy_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void copy_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// Shared memory holds two chunks of kChunk prepared rows.  While one chunk is walked the next one is on its way.
+// R lanes share a column and hold RPT rows each; a CTA of 128 threads owns 128 / R columns.
+template <int RPT, int R>
 __global__ void __launch_bounds__(kScanThreads)
 delta_rule_scan_kernel(ScanArgs a) {
-    extern __shared__ float smem[];
-    const int R = a.lanes, dpad = R * RPT, cols = kScanThreads / R;
-    float* q_s = smem;                       // [kChunk][dpad]
-    float* k_s = q_s + kChunk * dpad;
-    float* g_s = k_s + kChunk * dpad;
-    float* v_s = g_s + kChunk * dpad;        // [kChunk][cols]
-    float* b_s = v_s + kChunk * cols;        // [kChunk]
+    extern __shared__ __align__(16) float smem[];
+    constexpr int dpad = R * RPT, cols = kScanThreads / R;
+    const int per_chunk = kChunk * a.row;
 
     const int h = blockIdx.y, seq = blockIdx.z, col0 = blockIdx.x * cols;
-    const int kvh = h / (a.heads / a.kv_heads);
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tid = threadIdx.x;
     const int col = col0 + tid / R, r = tid % R;
     const bool live = col < a.d_v;
+    const int v_at = 3 * dpad + min(col, a.d_v - 1), b_at = 3 * dpad + a.d_v;
     const int first = a.cu_seqlens[seq], n = a.cu_seqlens[seq + 1] - first;
     float* S_g = a.state + (size_t)a.slots[seq] * a.slot_stride + (size_t)h * a.d_k * a.d_v;
-    const T* qkv = (const T*)a.qkv;
-    const T* beta = (const T*)a.beta;
-    const T* decay = (const T*)a.decay;
-    const float neg_rate = -expf(a.a_log[h]);
-    const int k_off = a.kv_heads * a.d_k, v_off = 2 * a.kv_heads * a.d_k;
+    const float* rows = a.rows + ((size_t)h * a.n_tokens + first) * a.row;
+
+    auto fetch = [&](int base, float* buf) {
+        const int floats = min(kChunk, n - base) * a.row;       // a multiple of 4; both ends 16-byte aligned
+        const float* src = rows + (size_t)base * a.row;
+        for (int i = tid * 4; i < floats; i += kScanThreads * 4) copy_async_16(buf + i, src + i);
+        copy_async_commit();
+    };
 
     float S[RPT];
 #pragma unroll
     for (int i = 0; i < RPT; ++i) {
-        const int row = r * RPT + i;
-        S[i] = (live && row < a.d_k) ? S_g[(size_t)row * a.d_v + col] : 0.f;
+        const int rw = i * R + r;
+        S[i] = (live && rw < a.d_k) ? S_g[(size_t)rw * a.d_v + col] : 0.f;
     }
 
+    fetch(0, smem);
+    int which = 0;
     for (int base = 0; base < n; base += kChunk) {
         const int m = min(kChunk, n - base);
-        __syncthreads();   // the chunk before has been walked
-        for (int tt = warp; tt < m; tt += kScanThreads / 32) {
-            const size_t t = (size_t)first + base + tt;
-            const T* qr = qkv + t * a.ld_qkv + (size_t)kvh * a.d_k;
-            const T* kr = qr + k_off;
-            float sq = 0.f, sk = 0.f;
-            for (int i = lane; i < a.d_k; i += 32) {
-                const float qv = to_f32<T>(qr[i]), kv = to_f32<T>(kr[i]);
-                sq += qv * qv;
-                sk += kv * kv;
-            }
-            sq = warp_sum(sq);
-            sk = warp_sum(sk);
-            const float fq = a.q_scale / sqrtf(sq + a.unit_eps), fk = 1.0f / sqrtf(sk + a.unit_eps);
-            const T* dr = decay + t * a.ld_decay + (size_t)h * a.d_k;
-            for (int i = lane; i < dpad; i += 32) {
-                float qv = 0.f, kv = 0.f, gv = 1.f;
-                if (i < a.d_k) {
-                    qv = to_f32<T>(qr[i]) * fq;
-                    kv = to_f32<T>(kr[i]) * fk;
-                    gv = expf(neg_rate * softplus(to_f32<T>(dr[i]) + a.dt_bias[(size_t)h * a.d_k + i]));
-                }
-                q_s[tt * dpad + i] = qv;
-                k_s[tt * dpad + i] = kv;
-                g_s[tt * dpad + i] = gv;
-            }
-            const T* vr = qkv + t * a.ld_qkv + v_off + (size_t)h * a.d_v + col0;
-            for (int c = lane; c < cols; c += 32) v_s[tt * cols + c] = (col0 + c < a.d_v) ? to_f32<T>(vr[c]) : 0.f;
-            if (lane == 0) b_s[tt] = 1.0f / (1.0f + expf(-to_f32<T>(beta[t * a.ld_beta + h])));
+        const float* buf = smem + which * per_chunk;
+        if (base + kChunk < n) {
+            fetch(base + kChunk, smem + (which ^ 1) * per_chunk);
+            copy_async_wait<1>();
+        } else {
+            copy_async_wait<0>();
         }
         __syncthreads();
+        float* out = a.out + ((size_t)first + base) * a.heads * a.d_v + (size_t)h * a.d_v + col;
+#pragma unroll 2
         for (int tt = 0; tt < m; ++tt) {
-            const float* qp = q_s + tt * dpad + r * RPT;
-            const float* kp = k_s + tt * dpad + r * RPT;
-            const float* gp = g_s + tt * dpad + r * RPT;
-            float dot = 0.f;
+            const float* qp = buf + tt * a.row + r;
+            const float* kp = qp + dpad;
+            const float* gp = kp + dpad;
+            const float v = buf[tt * a.row + v_at], beta = buf[tt * a.row + b_at], kq = buf[tt * a.row + b_at + 1];
+            // with S' = diag(g) S:  o = (S' + k u^T)^T q = S'^T q + u (k . q), so both sums over the rows are taken from
+            // S' in one pass and one round of exchanges, and k . q comes prepared with the token
+            float d[4] = {0.f, 0.f, 0.f, 0.f}, e[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int i = 0; i < RPT; ++i) {
-                S[i] *= gp[i];
-                dot += S[i] * kp[i];
+                S[i] *= gp[i * R];
+                d[i & 3] += S[i] * kp[i * R];
+                e[i & 3] += S[i] * qp[i * R];
             }
-            for (int o = R >> 1; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-            const float u = b_s[tt] * (v_s[tt * cols + tid / R] - dot);
-            float outv = 0.f;
+            float dot = (d[0] + d[1]) + (d[2] + d[3]), read = (e[0] + e[1]) + (e[2] + e[3]);
 #pragma unroll
-            for (int i = 0; i < RPT; ++i) {
-                S[i] += kp[i] * u;
-                outv += S[i] * qp[i];
+            for (int o = R >> 1; o > 0; o >>= 1) {
+                dot += __shfl_xor_sync(0xffffffffu, dot, o);
+                read += __shfl_xor_sync(0xffffffffu, read, o);
             }
-            for (int o = R >> 1; o > 0; o >>= 1) outv += __shfl_xor_sync(0xffffffffu, outv, o);
-            if (live && r == 0) a.out[((size_t)first + base + tt) * a.heads * a.d_v + (size_t)h * a.d_v + col] = outv;
+            const float u = beta * (v - dot);
+            if (live && r == 0) out[(size_t)tt * a.heads * a.d_v] = read + u * kq;
+#pragma unroll
+            for (int i = 0; i < RPT; ++i) S[i] += kp[i * R] * u;
         }
+        __syncthreads();   // the chunk has been walked: its buffer may be filled again
+        which ^= 1;
     }
 #pragma unroll
     for (int i = 0; i < RPT; ++i) {
-        const int row = r * RPT + i;
-        if (live && row < a.d_k) S_g[(size_t)row * a.d_v + col] = S[i];
+        const int rw = i * R + r;
+        if (live && rw < a.d_k) S_g[(size_t)rw * a.d_v + col] = S[i];
     }
 }
 
-template <typename T, int RPT>
+template <int RPT, int R>
 static int launch_scan(const ScanArgs& a, int n_seqs, cudaStream_t stream) {
-    const int cols = kScanThreads / a.lanes, dpad = a.lanes * RPT;
-    const size_t smem = sizeof(float) * ((size_t)kChunk * (3 * dpad + cols + 1));
-    auto kernel = delta_rule_scan_kernel<T, RPT>;
+    constexpr int cols = kScanThreads / R;
+    const size_t smem = sizeof(float) * 2 * (size_t)kChunk * a.row;
+    auto kernel = delta_rule_scan_kernel<RPT, R>;
     if (smem > 48 * 1024) {
         const int e = (int)cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != 0) return e;
@@ -192,6 +238,18 @@ static int launch_scan(const ScanArgs& a, int n_seqs, cudaStream_t stream) {
     dim3 grid((a.d_v + cols - 1) / cols, a.heads, n_seqs);
     kernel<<<grid, kScanThreads, smem, stream>>>(a);
     return launch_status();
+}
+
+template <int RPT>
+static int launch_scan_lanes(const ScanArgs& a, int lanes, int n_seqs, cudaStream_t stream) {
+    switch (lanes) {
+        case 1: return launch_scan<RPT, 1>(a, n_seqs, stream);
+        case 2: return launch_scan<RPT, 2>(a, n_seqs, stream);
+        case 4: return launch_scan<RPT, 4>(a, n_seqs, stream);
+        case 8: return launch_scan<RPT, 8>(a, n_seqs, stream);
+        case 16: return launch_scan<RPT, 16>(a, n_seqs, stream);
+    }
+    return kErrUnsupportedSize;
 }
 
 }  // namespace b200
@@ -214,9 +272,10 @@ extern "C" int b200_causal_conv_silu(const void* x, int ld_x, const float* w, fl
 }
 
 // The rows a thread holds (rows_per_thread: 8, 12, 16, 24 or 32) times the lanes that share a column (a power of two up
-// to 16) must cover d_k; b200_delta_rule_plan picks the pair for a d_k (0 when none fits).
+// to 16) must cover d_k; b200_delta_rule_plan picks the pair for a d_k (0 when none fits): the fewest rows beyond d_k,
+// then the fewest rows per thread (shared memory is read once per row and token by every warp).
 extern "C" int b200_delta_rule_plan(int d_k, int* rows_per_thread, int* lanes) {
-    const int options[5] = {16, 24, 12, 32, 8};
+    const int options[5] = {8, 12, 16, 24, 32};
     int best = 0, best_pad = 1 << 30;
     for (int oi = 0; oi < 5; ++oi)
         for (int R = 1; R <= 16; R *= 2) {
@@ -231,26 +290,38 @@ extern "C" int b200_delta_rule_plan(int d_k, int* rows_per_thread, int* lanes) {
     return best;
 }
 
+// Floats of one (token, head) row of the scratch that b200_delta_rule_scan needs: n_tokens * heads * this many
+// (0 for a d_k no kernel holds).
+extern "C" int b200_delta_rule_row(int d_k, int d_v) {
+    int rpt = 0, lanes = 0;
+    if (!b200_delta_rule_plan(d_k, &rpt, &lanes)) return 0;
+    return (3 * rpt * lanes + d_v + 2 + 3) / 4 * 4;
+}
+
 extern "C" int b200_delta_rule_scan(const void* qkv, int ld_qkv, const void* beta, int ld_beta, const void* decay,
                                     int ld_decay, const float* dt_bias, const float* a_log, float* state,
-                                    long long slot_stride, const int* slots, const int* cu_seqlens, float* out, int dtype,
-                                    int n_seqs, int heads, int kv_heads, int d_k, int d_v, float q_scale, float unit_eps,
-                                    cudaStream_t stream) {
-    if (n_seqs <= 0) return 0;
-    if (heads < 1 || kv_heads < 1 || heads % kv_heads || d_k < 1 || d_v < 1 || n_seqs > 65535 || heads > 65535)
+                                    long long slot_stride, const int* slots, const int* cu_seqlens, float* out,
+                                    float* scratch, int dtype, int n_tokens, int n_seqs, int heads, int kv_heads, int d_k,
+                                    int d_v, float q_scale, float unit_eps, cudaStream_t stream) {
+    if (n_seqs <= 0 || n_tokens <= 0) return 0;
+    if (heads < 1 || kv_heads < 1 || heads % kv_heads || d_k < 1 || d_v < 1 || n_seqs > 65535 || heads > 65535 || !scratch)
         return b200::kErrBadArgument;
     int rpt = 0, lanes = 0;
     if (!b200_delta_rule_plan(d_k, &rpt, &lanes)) return b200::kErrUnsupportedSize;
-    b200::ScanArgs a = {qkv, ld_qkv, beta, ld_beta, decay, ld_decay, dt_bias, a_log, state, (size_t)slot_stride, slots,
-                        cu_seqlens, out, heads, kv_heads, d_k, d_v, lanes, q_scale, unit_eps};
-#define B200_SCAN(RPT) B200_DISPATCH_DTYPE(dtype, T, return b200::launch_scan<T, RPT>(a, n_seqs, stream))
+    const int row = b200_delta_rule_row(d_k, d_v);
+    if ((uintptr_t)scratch % 16) return b200::kErrBadArgument;
+    b200::PrepareArgs p = {qkv, ld_qkv, beta, ld_beta, decay, ld_decay, dt_bias, a_log, scratch, n_tokens, heads, kv_heads,
+                           d_k, d_v, rpt * lanes, row, q_scale, unit_eps};
+    const long long units = (long long)n_tokens * heads;
+    B200_DISPATCH_DTYPE(dtype, T,
+        b200::delta_rule_prepare_kernel<T><<<(unsigned)((units + 3) / 4), 128, 0, stream>>>(p));
+    b200::ScanArgs a = {scratch, state, (size_t)slot_stride, slots, cu_seqlens, out, n_tokens, heads, d_k, d_v, row};
     switch (rpt) {
-        case 8: B200_SCAN(8);
-        case 12: B200_SCAN(12);
-        case 16: B200_SCAN(16);
-        case 24: B200_SCAN(24);
-        case 32: B200_SCAN(32);
+        case 8: return b200::launch_scan_lanes<8>(a, lanes, n_seqs, stream);
+        case 12: return b200::launch_scan_lanes<12>(a, lanes, n_seqs, stream);
+        case 16: return b200::launch_scan_lanes<16>(a, lanes, n_seqs, stream);
+        case 24: return b200::launch_scan_lanes<24>(a, lanes, n_seqs, stream);
+        case 32: return b200::launch_scan_lanes<32>(a, lanes, n_seqs, stream);
     }
-#undef B200_SCAN
     return b200::kErrUnsupportedSize;
 }

@@ -21,12 +21,21 @@ __device__ __forceinline__ float gated_pair(float gate, float up, int epilogue) 
     return (gate / (1.0f + expf(-gate))) * up;
 }
 
+// Several products of one shape side by side (gridDim.z of them): product z reads A + z a, W + z w and writes C + z c
+// (elements).  One head's small product after another, for mixers that carry every head through a matrix of its own.
+struct BatchStrides {
+    long long a, w, c;
+};
+
 constexpr int kTileM = 64, kTileN = 64, kTileK = 16, kGemmThreads = 256;
 
 template <typename TA, typename TW, typename TC>
 __global__ void __launch_bounds__(kGemmThreads)
 gemm_generic_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ W, int ldw, TC* __restrict__ C, int ldc,
-                    int M, int N, int K, int epilogue) {
+                    int M, int N, int K, int epilogue, BatchStrides batch) {
+    A += (size_t)blockIdx.z * batch.a;
+    W += (size_t)blockIdx.z * batch.w;
+    C += (size_t)blockIdx.z * batch.c;
     __shared__ float As[kTileK][kTileM + 4];
     __shared__ float Ws[kTileK][kTileN + 4];
     const int tid = threadIdx.x;
@@ -93,7 +102,10 @@ constexpr int kBigM = 128, kBigN = 128, kBigK = 16, kBigThreads = 256;
 template <typename TA, typename TW, typename TC>
 __global__ void __launch_bounds__(kBigThreads)
 gemm_generic_big_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ W, int ldw, TC* __restrict__ C, int ldc,
-                        int M, int N, int K, int epilogue) {
+                        int M, int N, int K, int epilogue, BatchStrides batch) {
+    A += (size_t)blockIdx.z * batch.a;
+    W += (size_t)blockIdx.z * batch.w;
+    C += (size_t)blockIdx.z * batch.c;
     __shared__ __align__(16) float As[kBigK][kBigM + 4];
     __shared__ __align__(16) float Ws[kBigK][kBigN + 4];
     const int tid = threadIdx.x;
@@ -195,7 +207,10 @@ __device__ __forceinline__ float reduce_by_halving(float (&v)[32], int lane) {
 template <typename TA, typename TW, typename TC, int MT>
 __global__ void __launch_bounds__(kFewThreads)
 gemm_fewrows_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ W, int ldw, TC* __restrict__ C, int ldc,
-                    int M, int N, int K, int epilogue) {
+                    int M, int N, int K, int epilogue, BatchStrides batch) {
+    A += (size_t)blockIdx.z * batch.a;
+    W += (size_t)blockIdx.z * batch.w;
+    C += (size_t)blockIdx.z * batch.c;
     __shared__ float part[kFewWarps][kFewRows * MT];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n0 = blockIdx.x * kFewRows;
@@ -252,40 +267,55 @@ gemm_fewrows_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ W,
 
 template <typename TA, typename TW, typename TC>
 static int launch_fewrows(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N, int K, int epilogue,
-                          cudaStream_t stream) {
-    const dim3 grid((N + kFewRows - 1) / kFewRows);
+                          int n_batch, BatchStrides batch, cudaStream_t stream) {
+    const dim3 grid((N + kFewRows - 1) / kFewRows, 1, n_batch);
     if (M <= 8)
-        gemm_fewrows_kernel<TA, TW, TC, 8><<<grid, kFewThreads, 0, stream>>>((const TA*)A, lda, (const TW*)W, ldw, (TC*)C, ldc, M, N, K, epilogue);
+        gemm_fewrows_kernel<TA, TW, TC, 8><<<grid, kFewThreads, 0, stream>>>((const TA*)A, lda, (const TW*)W, ldw, (TC*)C, ldc, M, N, K, epilogue, batch);
     else
-        gemm_fewrows_kernel<TA, TW, TC, 16><<<grid, kFewThreads, 0, stream>>>((const TA*)A, lda, (const TW*)W, ldw, (TC*)C, ldc, M, N, K, epilogue);
+        gemm_fewrows_kernel<TA, TW, TC, 16><<<grid, kFewThreads, 0, stream>>>((const TA*)A, lda, (const TW*)W, ldw, (TC*)C, ldc, M, N, K, epilogue, batch);
     return launch_status();
 }
 
 }  // namespace b200
 
-extern "C" int b200_gemm_generic(const void* A, int a_dtype, int lda, const void* W, int w_dtype, int ldw, void* C,
-                                 int c_dtype, int ldc, int M, int N, int K, int epilogue, cudaStream_t stream) {
-    if (M <= 0 || N <= 0) return 0;
+static int gemm_generic_launch(const void* A, int a_dtype, int lda, const void* W, int w_dtype, int ldw, void* C,
+                               int c_dtype, int ldc, int M, int N, int K, int epilogue, int n_batch,
+                               b200::BatchStrides batch, cudaStream_t stream) {
+    if (M <= 0 || N <= 0 || n_batch <= 0) return 0;
+    if (n_batch > 65535) return b200::kErrUnsupportedSize;
     if (K <= 0 || epilogue < 0 || epilogue > 3) return b200::kErrBadArgument;
     if (epilogue == 1 && c_dtype != b200::kF32) return b200::kErrBadArgument;
     if (epilogue >= 2 && (N & 1)) return b200::kErrBadArgument;
     // a decode step's few rows: rows of 4 elements at a time, when the rows start on such a boundary
     const size_t a_el = a_dtype == b200::kF32 ? 4 : 2, w_el = w_dtype == b200::kF32 ? 4 : 2;
-    if (M <= 16 && K % 4 == 0 && lda % 4 == 0 && ldw % 4 == 0 && ((uintptr_t)A % (4 * a_el)) == 0 && ((uintptr_t)W % (4 * w_el)) == 0) {
+    if (M <= 16 && K % 4 == 0 && lda % 4 == 0 && ldw % 4 == 0 && batch.a % 4 == 0 && batch.w % 4 == 0 && ((uintptr_t)A % (4 * a_el)) == 0 && ((uintptr_t)W % (4 * w_el)) == 0) {
         B200_DISPATCH_DTYPE(a_dtype, TA, B200_DISPATCH_DTYPE2(w_dtype, TW, B200_DISPATCH_DTYPE3(c_dtype, TC,
-            return b200::launch_fewrows<TA, TW, TC>(A, lda, W, ldw, C, ldc, M, N, K, epilogue, stream))));
+            return b200::launch_fewrows<TA, TW, TC>(A, lda, W, ldw, C, ldc, M, N, K, epilogue, n_batch, batch, stream))));
     }
     if (M >= b200::kBigM && (M + b200::kBigM - 1) / b200::kBigM <= 65535) {
-        dim3 big((N + b200::kBigN - 1) / b200::kBigN, (M + b200::kBigM - 1) / b200::kBigM);
+        dim3 big((N + b200::kBigN - 1) / b200::kBigN, (M + b200::kBigM - 1) / b200::kBigM, n_batch);
         B200_DISPATCH_DTYPE(a_dtype, TA, B200_DISPATCH_DTYPE2(w_dtype, TW, B200_DISPATCH_DTYPE3(c_dtype, TC,
             b200::gemm_generic_big_kernel<TA, TW, TC><<<big, b200::kBigThreads, 0, stream>>>(
-                (const TA*)A, lda, (const TW*)W, ldw, (TC*)C, ldc, M, N, K, epilogue))));
+                (const TA*)A, lda, (const TW*)W, ldw, (TC*)C, ldc, M, N, K, epilogue, batch))));
         return b200::launch_status();
     }
-    dim3 grid((N + b200::kTileN - 1) / b200::kTileN, (M + b200::kTileM - 1) / b200::kTileM);
+    dim3 grid((N + b200::kTileN - 1) / b200::kTileN, (M + b200::kTileM - 1) / b200::kTileM, n_batch);
     if (grid.y > 65535) return b200::kErrUnsupportedSize;
     B200_DISPATCH_DTYPE(a_dtype, TA, B200_DISPATCH_DTYPE2(w_dtype, TW, B200_DISPATCH_DTYPE3(c_dtype, TC,
         b200::gemm_generic_kernel<TA, TW, TC><<<grid, b200::kGemmThreads, 0, stream>>>(
-            (const TA*)A, lda, (const TW*)W, ldw, (TC*)C, ldc, M, N, K, epilogue))));
+            (const TA*)A, lda, (const TW*)W, ldw, (TC*)C, ldc, M, N, K, epilogue, batch))));
     return b200::launch_status();
+}
+
+extern "C" int b200_gemm_generic(const void* A, int a_dtype, int lda, const void* W, int w_dtype, int ldw, void* C,
+                                 int c_dtype, int ldc, int M, int N, int K, int epilogue, cudaStream_t stream) {
+    return gemm_generic_launch(A, a_dtype, lda, W, w_dtype, ldw, C, c_dtype, ldc, M, N, K, epilogue, 1, b200::BatchStrides{0, 0, 0}, stream);
+}
+
+// n_batch products of the same shape: product z uses A + z a_step, W + z w_step, C + z c_step (steps in elements).
+extern "C" int b200_gemm_generic_batched(const void* A, int a_dtype, int lda, long long a_step, const void* W, int w_dtype,
+                                         int ldw, long long w_step, void* C, int c_dtype, int ldc, long long c_step, int M,
+                                         int N, int K, int n_batch, cudaStream_t stream) {
+    return gemm_generic_launch(A, a_dtype, lda, W, w_dtype, ldw, C, c_dtype, ldc, M, N, K, 0, n_batch,
+                               b200::BatchStrides{a_step, w_step, c_step}, stream);
 }

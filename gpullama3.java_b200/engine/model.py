@@ -105,7 +105,10 @@ class CausalLM:
             out[names[path]] = spec
         return out
 
-    def new_cache(self, max_tokens: int, max_slots: int | None = None, window_slack: int = 0) -> SequenceCache:
+    def new_cache(self, max_tokens: int, max_slots: int | None = None, window_slack: int = 8192) -> SequenceCache:
+        """``window_slack``: the most tokens one sequence adds in one pass (a windowed cache group holds a window and
+        that many positions per sequence, never more than ``max_tokens`` in all); the default is the step function's
+        largest portion of one sequence."""
         return SequenceCache(self.cache_needs(), max_tokens=max_tokens, max_slots=max_slots, dtype=self.dtype,
                              device=self.device, window_slack=window_slack)
 

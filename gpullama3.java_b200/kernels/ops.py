@@ -43,6 +43,9 @@ _SIGNATURES = {
                                                    c_void_p]),
     "b200_gemm_generic": ("gemm_generic", [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int,
                                            c_int, c_int, c_int, c_int]),
+    "b200_gemm_generic_batched": ("gemm_generic", [c_void_p, c_int, c_int, ctypes.c_longlong, c_void_p, c_int, c_int,
+                                                   ctypes.c_longlong, c_void_p, c_int, c_int, ctypes.c_longlong, c_int, c_int,
+                                                   c_int, c_int]),
     "b200_gemm_decode": ("gemm_decode", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                          c_int]),
     "b200_gemm_decode_linked": ("gemm_decode", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
@@ -80,8 +83,8 @@ _SIGNATURES = {
     "b200_causal_conv_silu": ("delta_rule", [c_void_p, c_int, c_void_p, c_void_p, ctypes.c_longlong, c_void_p, c_void_p,
                                              c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int]),
     "b200_delta_rule_scan": ("delta_rule", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
-                                            ctypes.c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                                            c_int, c_int, c_float, c_float]),
+                                            ctypes.c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                            c_int, c_int, c_int, c_int, c_float, c_float]),
     "b200_argmax_rows": ("sampling", [c_void_p, c_int, c_void_p, c_int, c_int]),
     "b200_sample_rows": ("sampling", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_void_p]),
 }
@@ -275,6 +278,19 @@ def gemm_generic(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: in
     _check(_fn("b200_gemm_generic")(
         a.data_ptr(), dtype_code(a.dtype), a.stride(0), w.data_ptr(), dtype_code(w.dtype), w.stride(0), c.data_ptr(),
         dtype_code(c.dtype), c.stride(0), M, N, K, epilogue, _stream()), "gemm_generic")
+
+
+def gemm_per_head(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor) -> None:
+    """c[:, h n : (h + 1) n] = a[:, h k : (h + 1) k] @ w[h].T for every head h: a [T, H k], w [H, n, k], c [T, H n].
+    One launch of the plain kernel (32-bit FMA accumulation) for all heads."""
+    _dev(a, w, c)
+    H, n, k = w.shape
+    T = a.shape[0]
+    assert w.is_contiguous() and a.stride(1) == 1 and c.stride(1) == 1
+    assert tuple(a.shape) == (T, H * k) and tuple(c.shape) == (T, H * n)
+    _check(_fn("b200_gemm_generic_batched")(a.data_ptr(), dtype_code(a.dtype), a.stride(0), k, w.data_ptr(),
+                                            dtype_code(w.dtype), k, n * k, c.data_ptr(), dtype_code(c.dtype), c.stride(0), n,
+                                            T, n, k, H, _stream()), "gemm_per_head")
 
 
 def gemm_decode(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int = EPILOGUE_STORE) -> bool:
@@ -764,17 +780,21 @@ def delta_rule_supported(d_k: int) -> bool:
 def delta_rule_scan(qkv: torch.Tensor, beta: torch.Tensor, decay: torch.Tensor, dt_bias: torch.Tensor,
                     a_log: torch.Tensor, state: torch.Tensor, slots: torch.Tensor, cu_seqlens: torch.Tensor,
                     out: torch.Tensor, heads: int, kv_heads: int, d_k: int, d_v: int, q_scale: float,
-                    unit_eps: float) -> None:
+                    unit_eps: float, alloc=None) -> None:
     """The gated delta rule over a packed step.  qkv [T, 2 kv_heads d_k + heads d_v] (after the convolution), beta
     [T, >= heads] and decay [T, >= heads d_k] as the projections leave them, state float32 [slots, >= heads d_k d_v]
-    (updated in place), out float32 [T, heads d_v]."""
+    (updated in place), out float32 [T, heads d_v].  ``alloc(shape, dtype)``: where the scan's scratch (a row of
+    32-bit numbers per token and head) comes from."""
     _dev(qkv, beta, decay, dt_bias, a_log, state, slots, cu_seqlens, out)
     assert qkv.dtype == beta.dtype == decay.dtype and qkv.stride(1) == beta.stride(1) == decay.stride(1) == 1
     assert dt_bias.dtype == a_log.dtype == state.dtype == out.dtype == torch.float32 and out.is_contiguous()
     assert dt_bias.numel() == heads * d_k and a_log.numel() == heads and state.stride(1) == 1
     assert state.shape[1] >= heads * d_k * d_v and out.shape[1] == heads * d_v and out.shape[0] == qkv.shape[0]
+    lib = library("delta_rule")
+    shape = (heads, qkv.shape[0], int(lib.b200_delta_rule_row(c_int(d_k), c_int(d_v))))
+    scratch = alloc(shape, torch.float32) if alloc is not None else torch.empty(shape, dtype=torch.float32, device=qkv.device)
     _check(_fn("b200_delta_rule_scan")(qkv.data_ptr(), qkv.stride(0), beta.data_ptr(), beta.stride(0), decay.data_ptr(),
                                        decay.stride(0), dt_bias.data_ptr(), a_log.data_ptr(), state.data_ptr(),
                                        state.stride(0), slots.data_ptr(), cu_seqlens.data_ptr(), out.data_ptr(),
-                                       dtype_code(qkv.dtype), slots.numel(), heads, kv_heads, d_k, d_v, float(q_scale),
-                                       float(unit_eps), _stream()), "delta_rule_scan")
+                                       scratch.data_ptr(), dtype_code(qkv.dtype), qkv.shape[0], slots.numel(), heads,
+                                       kv_heads, d_k, d_v, float(q_scale), float(unit_eps), _stream()), "delta_rule_scan")

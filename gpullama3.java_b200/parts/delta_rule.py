@@ -103,7 +103,7 @@ class ChannelDeltaRule(Mixer):
         gate = self.g2.store(proj[:, self.g1_off:self.g1_off + self.gate_rank], ctx.dtype, ctx.empty)     # [T, H dv]
         o = ctx.empty((T, H * dv), torch.float32)
         ops.delta_rule_scan(qkv, proj[:, self.beta_off:], decay, self.dt_bias, self.a_log, state, ctx.slots_dev,
-                            ctx.cu_seqlens, o, H, G, dk, dv, dk ** -0.5, self.unit_eps)
+                            ctx.cu_seqlens, o, H, G, dk, dv, dk ** -0.5, self.unit_eps, alloc=ctx.empty)
         gated = ctx.empty((T, H * dv), ctx.dtype)
         ops.gated_rmsnorm(o, self.norm_weight, gate, gated, H, dv, self.norm_eps)
         return self.o.add_to(gated, residual, then_norm)

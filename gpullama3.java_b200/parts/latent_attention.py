@@ -5,7 +5,7 @@
     k_h = W_uk,h c ;  v_h = W_uv,h c ;  score = scale q_h . k_h ;  softmax ;  o_h = sum p v_h ;  W_o on the heads
 
 Since q_h . (W_uk,h c) = (W_uk,h^T q_h) . c and sum p (W_uv,h c) = W_uv,h (sum p c), the cache is never expanded:
-the queries are carried into the latent space (one small product per head), attention runs with ONE key/value head
+the queries are carried into the latent space (one small product per head, all heads in one launch), attention runs with ONE key/value head
 whose keys and values are both c (head size kv_rank, all query heads in its group), and the result is carried back
 through W_uv,h.  That is grouped-query attention over a paged cache, so the attention kernels and the cache group
 of ``GroupedQueryAttention`` serve it; the latent is stored twice, row-wise as the keys and transposed as the values.
@@ -75,8 +75,7 @@ class LatentAttention(Mixer):
         uk_t[:, :R] = uk.view(H, dk, R).transpose(1, 2)
         uv_w = torch.zeros((H, dv, D), dtype=uv.dtype, device=device)
         uv_w[:, :, :R] = uv.view(H, dv, R)
-        self.carry_in = [Linear(uk_t[h].contiguous()) for h in range(H)]
-        self.carry_out = [Linear(uv_w[h].contiguous()) for h in range(H)]
+        self.carry_in, self.carry_out = uk_t.contiguous(), uv_w.contiguous()   # [H, D, dk] and [H, dv, D]
         self.o = Linear(o.contiguous())
         self.norm_weights = torch.cat([tensors["dq_norm"].to(device=device, dtype=torch.float32),
                                        tensors["dkv_norm"].to(device=device, dtype=torch.float32)]).contiguous()
@@ -99,8 +98,7 @@ class LatentAttention(Mixer):
                                  cache.k, cache.v, 0, 1, D, 0, 0, write_cache=True)
         q = self.uq.store(c_q[:, :self.q_rank], ctx.dtype, ctx.empty)         # [T, H dk]
         carried = ctx.empty((T, H * D), ctx.dtype)                            # queries in the latent space
-        for h in range(H):
-            self.carry_in[h].into(q[:, h * dk:(h + 1) * dk], carried[:, h * D:(h + 1) * D])
+        ops.gemm_per_head(q, self.carry_in, carried)
         out = ctx.empty((T, H * D), ctx.dtype)
         if not fast.try_attention(carried, out, ctx, table, cache, self):
             n_rows = T * H
@@ -108,8 +106,7 @@ class LatentAttention(Mixer):
             ops.attention_paged(carried, carried.stride(0), out, ctx.positions, ctx.seq_ids, table, cache.k, cache.v,
                                 H, 1, D, self.window or 0, n_splits=splits)
         heads = ctx.empty((T, H * dv), ctx.dtype)
-        for h in range(H):
-            self.carry_out[h].into(out[:, h * D:(h + 1) * D], heads[:, h * dv:(h + 1) * dv])
+        ops.gemm_per_head(out, self.carry_out, heads)
         return self.o.add_to(heads, residual, then_norm)
 
 

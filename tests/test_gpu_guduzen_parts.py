@@ -187,3 +187,15 @@ def test_gated_rmsnorm(dtype):
     ops.gated_rmsnorm(x, w, gate, out, H, d, 1e-5)
     ref = plain.rms_normalise(x.cpu().to(F).view(T, H, d), 1e-5) * w.cpu().to(F) * torch.sigmoid(gate[:, :H * d].cpu().to(F).view(T, H, d))
     torch.testing.assert_close(out.cpu().to(F).view(T, H, d), ref, **_tol(dtype))
+
+
+@DTYPES
+@pytest.mark.parametrize("T", [1, 9, 70, 300])
+def test_products_per_head(dtype, T):
+    H, n, k = 3, 40, 24
+    a = _rand(T, H * k + 8, seed=1).to(dtype).cuda()[:, :H * k]      # rows wider than the heads: a row stride of its own
+    w = _rand(H, n, k, seed=2).to(dtype).cuda()
+    c = torch.empty(T, H * n, dtype=dtype, device="cuda")
+    ops.gemm_per_head(a, w, c)
+    ref = torch.einsum("thk,hnk->thn", a.cpu().to(F).view(T, H, k), w.cpu().to(F)).reshape(T, H * n)
+    torch.testing.assert_close(c.cpu().to(F), ref, **_tol(dtype))

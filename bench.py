@@ -382,7 +382,7 @@ def run_1b_f32(peaks, layers, warmup, context, batch):
 DESIGN_SIZES = {
     # width, feed-forward, heads / kv heads of size 64 (the delta and latent layers use the same head count), layers
     "s": dict(width=1024, ff=4096, heads=16, kv_heads=4, dim=64, layers=8, vocab=32768, window=1024, kv_rank=128, q_rank=384),
-    "m": dict(width=2048, ff=8192, heads=32, kv_heads=8, dim=64, layers=16, vocab=128256, window=1024, kv_rank=256, q_rank=768),
+    "m": dict(width=2048, ff=8192, heads=32, kv_heads=8, dim=64, layers=16, vocab=128256, window=1024, kv_rank=128, q_rank=768),
 }
 
 

@@ -5,6 +5,9 @@
 //     z <- z * weight[0 .. d)                       (optional: the norm's weight, shared by the rows)
 //     z <- z * mul                                  (a score scale folded into the queries, or 1)
 //     dst[dst_off + r d_pad .. + d_pad] = z, 0, ..., 0   (rows may be widened with zeros to the size a kernel takes)
+// A segment's rows go to a dense buffer (queries), or straight into the paged cache at the token's position: as key
+// rows ([page][kv_head][position][d_pad]) or as value rows (transposed, [page][kv_head][d_pad][position]), so that
+// a mixer without rotation needs no other kernel between its projection and attention.
 // Up to four such segments of a token's row are handled by one launch (queries, keys and values of an attention
 // layer; a latent that is stored once as keys and once as values).  A warp per (token, row).
 #include "common.cuh"
@@ -20,6 +23,15 @@ struct RowSegment {
     int norm;         // 1: divide by the row's root mean square
     int weight_off;   // into `weight`, -1: none
     float mul;
+    int target;       // 0: dst; 1: key rows of the cache; 2: value rows of the cache
+};
+struct CacheTarget {
+    const int* positions;
+    const int* seq_ids;
+    const int* page_table;
+    int table_stride;
+    void* k_pool;
+    void* v_pool;
 };
 struct RowSegments {
     RowSegment seg[kRowSegments];
@@ -30,7 +42,7 @@ struct RowSegments {
 template <typename T>
 __global__ void __launch_bounds__(kRowThreads)
 head_rows_kernel(const T* __restrict__ src, int ld_src, T* __restrict__ dst, int ld_dst, const float* __restrict__ bias,
-                 const float* __restrict__ weight, RowSegments segs, float eps) {
+                 const float* __restrict__ weight, RowSegments segs, float eps, CacheTarget cache) {
     const int t = blockIdx.x, lane = threadIdx.x & 31;
     int row = blockIdx.y * (kRowThreads / 32) + (threadIdx.x >> 5);
     if (row >= segs.total_rows) return;
@@ -54,35 +66,53 @@ head_rows_kernel(const T* __restrict__ src, int ld_src, T* __restrict__ dst, int
     }
     const float* w = g.weight_off >= 0 ? weight + g.weight_off : nullptr;
     T* o = dst + (size_t)t * ld_dst + g.dst_off + (size_t)row * g.d_pad;
+    size_t step = 1;
+    if (g.target != 0) {   // the row's place in the page of this token's position (n_rows = the cache's kv heads)
+        const int pos = cache.positions[t];
+        const size_t page = cache.page_table[(size_t)cache.seq_ids[t] * cache.table_stride + pos / kPageTokens];
+        const size_t head = (page * g.n_rows + row) * kPageTokens * g.d_pad;
+        if (g.target == 1) {
+            o = (T*)cache.k_pool + head + (size_t)(pos % kPageTokens) * g.d_pad;
+        } else {
+            o = (T*)cache.v_pool + head + (pos % kPageTokens);
+            step = kPageTokens;
+        }
+    }
     for (int e = lane; e < g.d_pad; e += 32) {
         float z = 0.f;
         if (e < g.d) {
             z = (to_f32<T>(x[e]) + (b ? b[e] : 0.f)) * factor;
             if (w) z *= w[e];
         }
-        o[e] = from_f32<T>(z);
+        o[(size_t)e * step] = from_f32<T>(z);
     }
 }
 
 }  // namespace b200
 
-// `segments`: n_segments records of nine 32-bit words each (src_off, n_rows, d, dst_off, d_pad, bias_off, norm,
-// weight_off, mul as float bits), read on the host.
+// `segments`: n_segments records of ten 32-bit words each (src_off, n_rows, d, dst_off, d_pad, bias_off, norm,
+// weight_off, mul as float bits, target), read on the host.  Segments with a cache target need positions, seq_ids,
+// page_table and the pools; their n_rows is the number of kv heads of the cache entry and d_pad its head size.
 extern "C" int b200_head_rows(const void* src, int ld_src, void* dst, int ld_dst, int dtype, const float* bias,
                               const float* weight, const int* segments, int n_segments, int n_tokens, float eps,
-                              cudaStream_t stream) {
+                              const int* positions, const int* seq_ids, const int* page_table, int table_stride,
+                              void* k_pool, void* v_pool, cudaStream_t stream) {
     if (n_tokens <= 0 || n_segments <= 0) return 0;
     if (n_segments > b200::kRowSegments) return b200::kErrBadArgument;
     b200::RowSegments segs = {};
     segs.n = n_segments;
     for (int i = 0; i < n_segments; ++i) {
-        const int* p = segments + 9 * i;
+        const int* p = segments + 10 * i;
         b200::RowSegment& g = segs.seg[i];
         g.src_off = p[0]; g.n_rows = p[1]; g.d = p[2]; g.dst_off = p[3]; g.d_pad = p[4];
         g.bias_off = p[5]; g.norm = p[6]; g.weight_off = p[7];
         union { int i; float f; } u;
         u.i = p[8];
         g.mul = u.f;
+        g.target = p[9];
+        if (g.target < 0 || g.target > 2) return b200::kErrBadArgument;
+        if (g.target != 0 && (!positions || !seq_ids || !page_table || (g.target == 1 ? !k_pool : !v_pool))) return b200::kErrBadArgument;
+        if (g.target == 0 && dst == nullptr) return b200::kErrBadArgument;
         if (g.n_rows < 0 || g.d < 1 || g.d_pad < g.d) return b200::kErrBadArgument;
         if ((g.bias_off >= 0 && bias == nullptr) || (g.weight_off >= 0 && weight == nullptr)) return b200::kErrBadArgument;
         segs.total_rows += g.n_rows;
@@ -91,8 +121,9 @@ extern "C" int b200_head_rows(const void* src, int ld_src, void* dst, int ld_dst
     const int per_cta = b200::kRowThreads / 32;
     dim3 grid(n_tokens, (segs.total_rows + per_cta - 1) / per_cta);
     if (grid.y > 65535) return b200::kErrUnsupportedSize;
+    const b200::CacheTarget cache = {positions, seq_ids, page_table, table_stride, k_pool, v_pool};
     B200_DISPATCH_DTYPE(dtype, T,
         b200::head_rows_kernel<T><<<grid, b200::kRowThreads, 0, stream>>>((const T*)src, ld_src, (T*)dst, ld_dst, bias,
-                                                                          weight, segs, eps));
+                                                                          weight, segs, eps, cache));
     return b200::launch_status();
 }

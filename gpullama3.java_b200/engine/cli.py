@@ -91,7 +91,8 @@ def describe_config(config) -> dict:
     import math
 
     specs = parameter_specs_by_checkpoint_name(config)
-    d = {"config": config.to_dict(), "parameters": sum(math.prod(s.shape) for s in specs.values()), "tensors": len(specs),
+    known = [s for s in specs.values() if min(s.shape, default=0) >= 0]   # (a size that only a checkpoint gives is not counted)
+    d = {"config": config.to_dict(), "parameters": sum(math.prod(s.shape) for s in known), "tensors": len(specs),
          "layers": len(config.layer_specs()), "schedule": [(e.layer, e.cache, e.writes_cache) for e in config.schedule()],
          "max_sequence_length": config.max_sequence_length(), "stop_token_ids": list(config.stop_token_ids)}
     for name in ("q_dim", "kv_dim"):

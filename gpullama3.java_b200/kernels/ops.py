@@ -74,8 +74,10 @@ _SIGNATURES = {
     "b200_streams_combine": ("streams", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int]),
     "b200_streams_read_norm": ("streams", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
                                            c_float]),
+    "b200_streams_step": ("streams", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                      c_int, c_int, c_float]),
     "b200_head_rows": ("head_rows", [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
-                                     c_float]),
+                                     c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
     "b200_softcap_rows": ("elementwise", [c_void_p, ctypes.c_longlong, c_float]),
     "b200_gated_activation": ("elementwise", [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int]),
     "b200_gated_rmsnorm": ("elementwise", [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
@@ -691,28 +693,61 @@ def streams_read_norm(x: torch.Tensor, read: torch.Tensor, weight: torch.Tensor,
                                          width, float(eps), _stream()), "streams_read_norm")
 
 
+def streams_step(x: torch.Tensor, mix: torch.Tensor, write: torch.Tensor, y: torch.Tensor, read: torch.Tensor | None = None,
+                 weight: torch.Tensor | None = None, out: torch.Tensor | None = None, eps: float = 0.0) -> None:
+    """One sublayer's write-back and the next one's read in one pass: x[t, j] <- sum_a mix[a, j] x[t, a] + write[j] y[t]
+    in place, y <- 0, and with ``read``: out[t] = weight * u / sqrt(mean(u^2) + eps), u = sum_j read[j] x[t, j]."""
+    _dev(x, mix, write, y, read, weight, out)
+    T, s, width = x.shape
+    assert x.dtype == mix.dtype == write.dtype == y.dtype == torch.float32 and x.is_contiguous() and y.is_contiguous()
+    assert mix.is_contiguous() and mix.numel() == s * s and write.numel() == s and tuple(y.shape) == (T, width)
+    if read is not None:
+        assert read.dtype == weight.dtype == torch.float32 and read.numel() == s and weight.numel() == width
+        assert out.is_contiguous() and tuple(out.shape) == (T, width)
+    _check(_fn("b200_streams_step")(x.data_ptr(), mix.data_ptr(), write.data_ptr(), y.data_ptr(),
+                                    read.data_ptr() if read is not None else None,
+                                    weight.data_ptr() if read is not None else None,
+                                    out.data_ptr() if read is not None else None,
+                                    dtype_code(out.dtype) if read is not None else 0, T, s, width, float(eps), _stream()),
+           "streams_step")
+
+
 # --------------------------------------------------------------------------- rows of a projection, per head
+TO_ROWS, TO_CACHE_KEYS, TO_CACHE_VALUES = 0, 1, 2
+
+
 def head_row_segment(src_off: int, n_rows: int, d: int, dst_off: int, d_pad: int | None = None, bias_off: int = -1,
-                     norm: bool = False, weight_off: int = -1, mul: float = 1.0) -> list[int]:
+                     norm: bool = False, weight_off: int = -1, mul: float = 1.0, target: int = TO_ROWS) -> list[int]:
     """One segment of ``head_rows``: ``n_rows`` rows of ``d`` numbers from column ``src_off`` on, each (+ bias)
-    (normalised) (* weight) * mul, written ``d_pad`` wide (zeros behind the ``d``) from column ``dst_off`` on."""
+    (normalised) (* weight) * mul, written ``d_pad`` wide (zeros behind the ``d``) from column ``dst_off`` on, or with
+    ``target`` TO_CACHE_KEYS / TO_CACHE_VALUES into the cache page of the token's position (``n_rows`` = the cache
+    entry's kv heads, ``d_pad`` its head size)."""
     import struct
 
     return [src_off, n_rows, d, dst_off, d if d_pad is None else d_pad, bias_off, 1 if norm else 0, weight_off,
-            struct.unpack("<i", struct.pack("<f", float(mul)))[0]]
+            struct.unpack("<i", struct.pack("<f", float(mul)))[0], target]
 
 
-def head_rows(src: torch.Tensor, dst: torch.Tensor, segments, eps: float = 0.0, bias: torch.Tensor | None = None,
-              weight: torch.Tensor | None = None) -> None:
-    """``segments``: a ctypes array made by ``head_row_segments`` (at most four segments)."""
+def head_rows(src: torch.Tensor, dst: torch.Tensor | None, segments, eps: float = 0.0, bias: torch.Tensor | None = None,
+              weight: torch.Tensor | None = None, cache=None) -> None:
+    """``segments``: a ctypes array made by ``head_row_segments`` (at most four segments).  ``cache``: (positions,
+    seq_ids, page_table, k_pool, v_pool) for segments that go into the paged cache; ``dst`` may be None when all do."""
     _dev(src, dst, bias, weight)
-    assert src.dtype == dst.dtype and src.stride(1) == 1 and dst.stride(1) == 1 and src.shape[0] == dst.shape[0]
+    assert src.stride(1) == 1
+    assert dst is None or (src.dtype == dst.dtype and dst.stride(1) == 1 and src.shape[0] == dst.shape[0])
     assert bias is None or (bias.dtype == torch.float32 and bias.is_contiguous())
     assert weight is None or (weight.dtype == torch.float32 and weight.is_contiguous())
-    _check(_fn("b200_head_rows")(src.data_ptr(), src.stride(0), dst.data_ptr(), dst.stride(0), dtype_code(src.dtype),
-                                 bias.data_ptr() if bias is not None else None,
-                                 weight.data_ptr() if weight is not None else None, ctypes.addressof(segments),
-                                 len(segments) // 9, src.shape[0], float(eps), _stream()), "head_rows")
+    pos = seq = table = k_pool = v_pool = None
+    if cache is not None:
+        pos, seq, table, k_pool, v_pool = cache
+        _dev(pos, seq, table, k_pool, v_pool)
+        assert pos.dtype == seq.dtype == table.dtype == torch.int32 and table.dim() == 2 and table.is_contiguous()
+        assert k_pool.dtype == v_pool.dtype == src.dtype and k_pool.is_contiguous() and v_pool.is_contiguous()
+    ptr = lambda t: t.data_ptr() if t is not None else None
+    _check(_fn("b200_head_rows")(src.data_ptr(), src.stride(0), ptr(dst), dst.stride(0) if dst is not None else 0,
+                                 dtype_code(src.dtype), ptr(bias), ptr(weight), ctypes.addressof(segments),
+                                 len(segments) // 10, src.shape[0], float(eps), ptr(pos), ptr(seq), ptr(table),
+                                 table.shape[1] if table is not None else 0, ptr(k_pool), ptr(v_pool), _stream()), "head_rows")
 
 
 def head_row_segments(*segments: list[int]):

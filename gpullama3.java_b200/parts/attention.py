@@ -121,11 +121,17 @@ class GroupedQueryAttention(Mixer):
         mul = (self.scale if self.scale is not None else dk ** -0.5) * D ** 0.5
         norm = self.qk_norm_eps is not None
         b = (lambda off: off) if self.bias else (lambda off: -1)
+        # without rotation the finished keys and values go straight into their cache pages; with it they go to the
+        # dense rows that the rotation kernel reads
+        direct = not self.position.rotary_dim
+        keys, values = (ops.TO_CACHE_KEYS, ops.TO_CACHE_VALUES) if direct else (ops.TO_ROWS, ops.TO_ROWS)
         segs = [ops.head_row_segment(0, H, dk, 0, D, b(0), norm, -1, mul)]
         if not self.shares_cache:
-            segs.append(ops.head_row_segment(H * dk, G, dk, H * D, D, b(H * dk), norm))
-            segs.append(ops.head_row_segment((H + G) * dk, G, dv, (H + G) * D, D, b((H + G) * dk)))
+            segs.append(ops.head_row_segment(H * dk, G, dk, H * D, D, b(H * dk), norm, target=keys))
+            segs.append(ops.head_row_segment((H + G) * dk, G, dv, (H + G) * D, D, b((H + G) * dk), target=values))
         self.segments = ops.head_row_segments(*segs)
+        self.query_segment = ops.head_row_segments(segs[0])
+        self.writes_direct = direct
 
     def takes_scaled_rows(self, ctx: StepContext) -> bool:
         return not self.finishes_heads and ctx.all_decode and self.qkv.links_with(ctx.n_tokens, ctx.dtype)
@@ -138,11 +144,16 @@ class GroupedQueryAttention(Mixer):
             if writes_cache and self.shares_cache:
                 raise ConfigError("a mixer without key and value projections cannot write a cache entry")
             raw = self.qkv.store(x, ctx.dtype, ctx.empty)
-            qkv = ctx.empty((x.shape[0], self.q_dim + 2 * self.kv_dim), ctx.dtype)   # (a reader leaves the key and value columns unused)
-            ops.head_rows(raw, qkv, self.segments, self.qk_norm_eps or 0.0, self.head_bias)
-            ops.rope_cache_write(qkv, ctx.positions, ctx.seq_ids, table, self.position.inverse_frequencies(x.device),
-                                 cache.k, cache.v, self.n_heads, self.n_kv_heads, self.head_dim,
-                                 self.position.rotary_dim, self.position.pairing, write_cache=writes_cache)
+            if self.writes_direct:
+                qkv = ctx.empty((x.shape[0], self.q_dim), ctx.dtype)
+                ops.head_rows(raw, qkv, self.segments if writes_cache else self.query_segment, self.qk_norm_eps or 0.0,
+                              self.head_bias, cache=(ctx.positions, ctx.seq_ids, table, cache.k, cache.v) if writes_cache else None)
+            else:
+                qkv = ctx.empty((x.shape[0], self.q_dim + 2 * self.kv_dim), ctx.dtype)   # (a reader leaves the key and value columns unused)
+                ops.head_rows(raw, qkv, self.segments, self.qk_norm_eps or 0.0, self.head_bias)
+                ops.rope_cache_write(qkv, ctx.positions, ctx.seq_ids, table, self.position.inverse_frequencies(x.device),
+                                     cache.k, cache.v, self.n_heads, self.n_kv_heads, self.head_dim,
+                                     self.position.rotary_dim, self.position.pairing, write_cache=writes_cache)
         elif isinstance(x, torch.Tensor) and not ctx.all_decode:
             # a prompt pass: projection, rotation and cache write as one product where its epilogue can do all three
             qkv = ctx.empty((x.shape[0], self.qkv.out_features), ctx.dtype)

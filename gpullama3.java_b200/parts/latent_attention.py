@@ -21,7 +21,6 @@ from ..weights.loader import ParamSpec
 from .attention import kernel_head_dim
 from .base import Mixer, StepContext, register_mixer
 from .linear import Linear
-from .position import NoPositionEncoding
 
 
 class LatentAttention(Mixer):
@@ -42,7 +41,6 @@ class LatentAttention(Mixer):
         if window is not None and window < 1:
             raise ConfigError(f"window {window} must be at least 1 (or None for no window)")
         self.n_kv_heads, self.window = 1, window
-        self.position = NoPositionEncoding()
         self.q_pad = -(-self.q_rank // 8) * 8
 
     def parameters(self):
@@ -82,8 +80,9 @@ class LatentAttention(Mixer):
         mul = self.scale * D ** 0.5   # the attention kernels divide every score by sqrt(their head size)
         qr = self.q_rank
         self.query_segment = ops.head_row_segments(ops.head_row_segment(0, 1, qr, 0, self.q_pad, -1, True, 0, mul))   # c_q
-        self.latent_segments = ops.head_row_segments(ops.head_row_segment(qr, 1, R, 0, D, -1, True, qr),   # c, read as keys
-                                                     ops.head_row_segment(qr, 1, R, D, D, -1, True, qr))   # c, read as values
+        self.latent_segments = ops.head_row_segments(   # c, once as a key row and once as a value row of its cache page
+            ops.head_row_segment(qr, 1, R, 0, D, -1, True, qr, target=ops.TO_CACHE_KEYS),
+            ops.head_row_segment(qr, 1, R, 0, D, -1, True, qr, target=ops.TO_CACHE_VALUES))
 
     def forward(self, x, ctx: StepContext, cache: KVView, residual, writes_cache=True, then_norm=None):
         H, dk, dv, D, T = self.n_heads, self.key_dim, self.value_dim, self.head_dim, x.shape[0]
@@ -92,10 +91,8 @@ class LatentAttention(Mixer):
         c_q = ctx.empty((T, self.q_pad), ctx.dtype)
         ops.head_rows(down, c_q, self.query_segment, self.norm_eps, None, self.norm_weights)
         if writes_cache:
-            kv = ctx.empty((T, 2 * D), ctx.dtype)                             # the latent twice: as a key row, as a value row
-            ops.head_rows(down, kv, self.latent_segments, self.norm_eps, None, self.norm_weights)
-            ops.rope_cache_write(kv, ctx.positions, ctx.seq_ids, table, self.position.inverse_frequencies(x.device),
-                                 cache.k, cache.v, 0, 1, D, 0, 0, write_cache=True)
+            ops.head_rows(down, None, self.latent_segments, self.norm_eps, None, self.norm_weights,
+                          cache=(ctx.positions, ctx.seq_ids, table, cache.k, cache.v))
         q = self.uq.store(c_q[:, :self.q_rank], ctx.dtype, ctx.empty)         # [T, H dk]
         carried = ctx.empty((T, H * D), ctx.dtype)                            # queries in the latent space
         ops.gemm_per_head(q, self.carry_in, carried)

@@ -61,6 +61,29 @@ class StreamConnection(Part):
     def write_back(self, residual: torch.Tensor, y: torch.Tensor) -> None:
         ops.streams_combine(residual, residual, self.mix, self.write, y)
 
+    def step(self, residual: torch.Tensor, y: torch.Tensor, then: "StreamRead | None", ctx: StepContext, alloc):
+        """This sublayer's write-back (which also clears ``y`` for the next sublayer's product) and, in the same
+        kernel, the read and norm of the sublayer that runs next (``then``); returns that sublayer's input rows, or
+        None when nothing runs next."""
+        if then is None:
+            ops.streams_step(residual, self.mix, self.write, y)
+            return None
+        weight, eps, dim = _norm_form(then.norm)
+        out = alloc((residual.shape[0], dim), ctx.dtype)
+        ops.streams_step(residual, self.mix, self.write, y, then.connection.read, weight, out, eps)
+        return out
+
+
+class StreamRead:
+    """How a connected sublayer takes its input: the read weights of its connection and the norm behind them.  A
+    block hands this out as its first norm, so that the block before it can do the read in its own last kernel."""
+
+    def __init__(self, norm, connection: StreamConnection):
+        self.norm, self.connection = norm, connection
+
+    def row_factor_form(self):
+        return self.norm.row_factor_form()
+
 
 _ones: dict = {}
 
@@ -126,24 +149,39 @@ class ConnectedBlock(Block):
         return all(p.pad_safe for p in all_parts(self).values())
 
     def first_norm(self):
-        return self.mixer_norm
+        if self.mixer_connection is None:
+            return self.mixer_norm
+        return StreamRead(self.mixer_norm, self.mixer_connection)
 
-    def _sublayer(self, residual, ctx, norm, connection, run):
-        if connection is None:
-            run(norm.forward(residual, ctx.dtype, alloc=ctx.empty), residual)
-            return
-        x = connection.read_norm(residual, norm, ctx)
-        y = ctx.empty((residual.shape[0], residual.shape[2]), torch.float32)
-        y.zero_()   # the sublayer's last product adds into it, as it would into a residual stream
-        run(x, y)
-        connection.write_back(residual, y)
+    def takes_scaled_rows(self, ctx: StepContext) -> bool:
+        """With stream connections the block takes its first input from the block before it (``x_in``) and leaves the
+        next block's (``then_norm``, that block's ``StreamRead``): a write-back and the read behind it are one kernel."""
+        return self.mixer_connection is not None
 
-    def forward(self, residual, ctx: StepContext, cache, writes_cache=True):
-        self._sublayer(residual, ctx, self.mixer_norm, self.mixer_connection,
-                       lambda x, y: self.mixer.forward(x, ctx, cache, y, writes_cache))
+    def forward(self, residual, ctx: StepContext, cache, writes_cache=True, x_in=None, then_norm=None):
+        if self.mixer_connection is None:     # one residual stream: x <- x + sublayer(norm(x))
+            self.mixer.forward(self.mixer_norm.forward(residual, ctx.dtype, alloc=ctx.empty), ctx, cache, residual, writes_cache)
+            if self.feed_forward is not None:
+                self.feed_forward.forward(self.feed_forward_norm.forward(residual, ctx.dtype, alloc=ctx.empty), ctx, residual)
+            return None
+        # what a sublayer's last product adds into, as it would into a residual stream: one buffer per pass, cleared
+        # by the kernel that consumes it
+        y = ctx.extras.get("stream sublayer result")
+        if y is None:
+            y = ctx.extras["stream sublayer result"] = torch.zeros((residual.shape[0], residual.shape[2]),
+                                                                   dtype=torch.float32, device=residual.device)
+        x = x_in if x_in is not None else self.mixer_connection.read_norm(residual, self.mixer_norm, ctx)
+        self.mixer.forward(x, ctx, cache, y, writes_cache)
+        last = self.mixer_connection
         if self.feed_forward is not None:
-            self._sublayer(residual, ctx, self.feed_forward_norm, self.feed_forward_connection,
-                           lambda x, y: self.feed_forward.forward(x, ctx, y))
+            x = last.step(residual, y, StreamRead(self.feed_forward_norm, self.feed_forward_connection), ctx, ctx.empty)
+            self.feed_forward.forward(x, ctx, y)
+            last = self.feed_forward_connection
+        if then_norm is not None and not isinstance(then_norm, StreamRead):
+            then_norm = None
+        # (rows handed to the next block outlive this block's workspace: they come from the allocator)
+        return last.step(residual, y, then_norm, ctx,
+                         lambda shape, dtype: torch.empty(shape, dtype=dtype, device=residual.device))
 
 
 register_part("connection", "streams", StreamConnection)

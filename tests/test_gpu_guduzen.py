@@ -159,3 +159,30 @@ def test_greedy_generation_through_the_engine(setup, dtype):
             row = logits[len(p) - 1 + i]
             slack = 1e-4 * float(row.abs().max()) if dtype == torch.float32 else 0.05 * float(row.abs().max())
             assert float(row.max() - row[tok]) <= slack, (dtype, i, tok, int(torch.argmax(row)))
+
+
+def test_command_line(setup, tmp_path):
+    """``bin/llama-b200`` on a Guduzen folder: greedy tokens are the plain implementation's, the layer plan is shown,
+    random weights fill a configuration, and sampling with a temperature runs."""
+    import json
+
+    d, cfg, weights, requests, refs = setup
+    env = dict(os.environ, PYTHON=sys.executable)
+    prompt = requests["r2"][:9]
+    cmd = [str(ROOT / "bin" / "llama-b200"), "--model", str(d), "--dtype", "float32", "--temperature", "0", "-n", "5",
+           "--stream", "false", "--prompt", " ".join(map(str, prompt))]
+    p = subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=900)
+    assert p.returncode == 0, p.stderr[-2000:]
+    got = list(map(int, p.stdout.split()))
+    assert len(got) == 5
+    logits = plain_guduzen.forward(cfg, weights, prompt + got)
+    for i, tok in enumerate(got):
+        row = logits[len(prompt) - 1 + i]
+        assert float(row.max() - row[tok]) <= 1e-4 * float(row.abs().max())
+    p = subprocess.run(cmd + ["--show-config"], capture_output=True, text=True, env=env, timeout=900)
+    assert p.returncode == 0 and '"architecture": "Guduzen"' in p.stdout + p.stderr, p.stderr[-2000:]
+    (tmp_path / "config.json").write_text(json.dumps(cfg))
+    p = subprocess.run([str(ROOT / "bin" / "llama-b200"), "--config", str(tmp_path / "config.json"), "--random-weights", "3",
+                        "--prompt", "1 2 3", "--prompt", "4 5", "-n", "4", "--seed", "1", "--temperature", "0.8",
+                        "--top-p", "0.9"], capture_output=True, text=True, env=env, timeout=900)
+    assert p.returncode == 0 and len(p.stdout.split()) == 8, p.stderr[-2000:]

@@ -199,3 +199,53 @@ def test_products_per_head(dtype, T):
     ops.gemm_per_head(a, w, c)
     ref = torch.einsum("thk,hnk->thn", a.cpu().to(F).view(T, H, k), w.cpu().to(F)).reshape(T, H * n)
     torch.testing.assert_close(c.cpu().to(F), ref, **_tol(dtype))
+
+
+@pytest.mark.parametrize("streams, width, T", [(1, 48, 5), (3, 100, 7), (2, 2500, 3)])
+def test_streams_step(streams, width, T):
+    """Write-back, clearing of the sublayer result and the next read with its norm, in one kernel."""
+    xs = _rand(T, streams, width, seed=2).cuda()
+    lst = [xs[:, a].cpu().to(F) for a in range(streams)]
+    W = {"h.mix": _rand(streams, streams, seed=4).to(F), "h.out": _rand(streams, seed=5).to(F)}
+    read, nw = _rand(streams, seed=3), _rand(width, seed=6) * 0.3
+    y = _rand(T, width, seed=7).cuda()
+    ref = plain.connect(lst, W, "h.", y.cpu().to(F))
+    out = torch.empty(T, width, device="cuda")
+    ops.streams_step(xs, W["h.mix"].float().cuda(), W["h.out"].float().cuda(), y, read.cuda(), (1 + nw).cuda(), out, 1e-5)
+    for j in range(streams):
+        torch.testing.assert_close(xs[:, j].cpu().to(F), ref[j], rtol=2e-5, atol=2e-5)
+    u = sum(read[a].to(F) * ref[a] for a in range(streams))
+    torch.testing.assert_close(out.cpu().to(F), plain.offset_norm(u, nw.to(F), 1e-5), rtol=5e-5, atol=5e-5)
+    assert float(y.abs().max()) == 0.0
+    y2 = _rand(T, width, seed=8).cuda()
+    ref2 = plain.connect(ref, W, "h.", y2.cpu().to(F))
+    ops.streams_step(xs, W["h.mix"].float().cuda(), W["h.out"].float().cuda(), y2)       # nothing runs next
+    for j in range(streams):
+        torch.testing.assert_close(xs[:, j].cpu().to(F), ref2[j], rtol=5e-5, atol=5e-5)
+    assert float(y2.abs().max()) == 0.0
+
+
+@DTYPES
+def test_head_rows_into_cache_pages(dtype):
+    """Keys as rows and values transposed, each at its token's position in the page its sequence's table names."""
+    T, G, dk, dv, D, n_pages = 7, 2, 24, 16, 32, 5
+    src = _rand(T, G * dk + G * dv, seed=1).to(dtype).cuda()
+    positions = torch.tensor([62, 63, 64, 65, 0, 1, 130], dtype=torch.int32, device="cuda")
+    seq_ids = torch.tensor([0, 0, 0, 0, 1, 1, 1], dtype=torch.int32, device="cuda")
+    table = torch.tensor([[3, 1, 0], [4, 0, 2]], dtype=torch.int32, device="cuda")
+    k_pool = torch.full((n_pages, G, 64, D), 9.0, dtype=dtype, device="cuda")
+    v_pool = torch.full((n_pages, G, D, 64), 9.0, dtype=dtype, device="cuda")
+    segs = ops.head_row_segments(ops.head_row_segment(0, G, dk, 0, D, -1, True, target=ops.TO_CACHE_KEYS),
+                                 ops.head_row_segment(G * dk, G, dv, 0, D, target=ops.TO_CACHE_VALUES))
+    ops.head_rows(src, None, segs, 1e-6, cache=(positions, seq_ids, table, k_pool, v_pool))
+    k_ref = plain.rms_normalise(src[:, :G * dk].cpu().to(F).view(T, G, dk), 1e-6)
+    v_ref = src[:, G * dk:].cpu().to(F).view(T, G, dv)
+    written_k = torch.zeros(n_pages, G, 64, dtype=torch.bool)
+    for t in range(T):
+        pos, page = int(positions[t]), int(table[int(seq_ids[t]), int(positions[t]) // 64])
+        torch.testing.assert_close(k_pool[page, :, pos % 64, :dk].cpu().to(F), k_ref[t], **_tol(dtype))
+        torch.testing.assert_close(v_pool[page, :, :dv, pos % 64].cpu().to(F), v_ref[t], **_tol(dtype))
+        assert float(k_pool[page, :, pos % 64, dk:].abs().max()) == 0.0 and float(v_pool[page, :, dv:, pos % 64].abs().max()) == 0.0
+        written_k[page, :, pos % 64] = True
+    assert bool((k_pool.cpu()[~written_k] == 9.0).all())      # nothing else was touched
+    assert int((v_pool.cpu() != 9.0).sum()) == T * G * D

@@ -1,32 +1,14 @@
 // Small per-element and per-row kernels that several parts share.
 //   softcap_rows       x <- cap * tanh(x / cap), in place on 32-bit logits
-//   gated_activation   out[t, j] = act(in[t, 2j]) * in[t, 2j + 1]   (gate and up values side by side, as the gated
-//                      feed-forward's product leaves them when its own epilogue does not apply the activation)
 //   gated_rmsnorm      out[t, h, :] = x[t, h, :] / sqrt(mean(x^2) + eps) * w * sigmoid(gate[t, h, :])
 //                      per (token, head) row of 32-bit numbers: the output norm of a recurrent mixer
-// Activations: 0 SiLU z / (1 + exp(-z)); 1 GELU in its tanh form 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))).
 #include "common.cuh"
 
 namespace b200 {
 
-__device__ __forceinline__ float activation(float z, int kind) {
-    if (kind == 1) return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
-    return z / (1.0f + expf(-z));
-}
-
 __global__ void softcap_kernel(float* __restrict__ x, size_t n, float cap) {
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
         x[i] = cap * tanhf(x[i] / cap);
-}
-
-template <typename T>
-__global__ void gated_activation_kernel(const T* __restrict__ in, int ld_in, T* __restrict__ out, int ld_out, int n_out,
-                                        int kind) {
-    const int t = blockIdx.y;
-    const int j = blockIdx.x * blockDim.x + threadIdx.x;
-    if (j >= n_out) return;
-    const T* p = in + (size_t)t * ld_in + 2 * j;
-    out[(size_t)t * ld_out + j] = from_f32<T>(activation(to_f32<T>(p[0]), kind) * to_f32<T>(p[1]));
 }
 
 // a warp per (token, head) row
@@ -57,20 +39,6 @@ extern "C" int b200_softcap_rows(float* x, long long n, float cap, cudaStream_t 
     if (!(cap > 0.f)) return b200::kErrBadArgument;
     const long long blocks = (n + 255) / 256;
     b200::softcap_kernel<<<(int)(blocks < 148 * 16 ? blocks : 148 * 16), 256, 0, stream>>>(x, (size_t)n, cap);
-    return b200::launch_status();
-}
-
-extern "C" int b200_gated_activation(const void* in, int ld_in, void* out, int ld_out, int dtype, int n_tokens,
-                                     int n_out, int kind, cudaStream_t stream) {
-    if (n_tokens <= 0 || n_out <= 0) return 0;
-    if (kind < 0 || kind > 1) return b200::kErrBadArgument;
-    if (n_tokens > 65535) {
-        // (grid.y holds the tokens; a pass is cut well below this)
-        return b200::kErrUnsupportedSize;
-    }
-    dim3 grid((n_out + 255) / 256, n_tokens);
-    B200_DISPATCH_DTYPE(dtype, T,
-        b200::gated_activation_kernel<T><<<grid, 256, 0, stream>>>((const T*)in, ld_in, (T*)out, ld_out, n_out, kind));
     return b200::launch_status();
 }
 

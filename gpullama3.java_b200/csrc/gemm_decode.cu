@@ -59,6 +59,8 @@ struct NormLink {
     __nv_bfloat16* out_act;     // [M][ld_out_act]
     int ld_out_act;
     float* out_partials;        // [M][gridDim.x]
+    // the gated epilogue's activation of the gate value: 0 SiLU, 1 GELU in its tanh form
+    int gate_act;
 };
 
 // LINK: the product is a half of a split norm (the plain product is compiled without any of that)
@@ -219,7 +221,10 @@ gemm_decode_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bflo
             const int token = idx / (ROWS / 2), pair = idx % (ROWS / 2);
             if (token < M && row0 + 2 * pair + 1 < N) {
                 const float gate = fin[token][2 * pair], up = fin[token][2 * pair + 1];
-                C[(size_t)token * ldc + (row0 >> 1) + pair] = from_f32<TC>((gate / (1.0f + expf(-gate))) * up);
+                const float act = link.gate_act == 1
+                                      ? 0.5f * gate * (1.0f + tanhf(0.7978845608028654f * (gate + 0.044715f * gate * gate * gate)))
+                                      : gate / (1.0f + expf(-gate));
+                C[(size_t)token * ldc + (row0 >> 1) + pair] = from_f32<TC>(act * up);
             }
         }
     }
@@ -288,8 +293,13 @@ static int decode_rows_per_cta(int M, int N) {
 }
 
 static int gemm_decode_launch(const void* A, int lda, const void* W, int ldw, void* C, int c_dtype, int ldc, int M, int N,
-                              int K, int epilogue, const NormLink& link, cudaStream_t stream) {
+                              int K, int epilogue, const NormLink& link_in, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
+    NormLink link = link_in;
+    if (epilogue == 3) {   // the gated epilogue with the other activation
+        link.gate_act = 1;
+        epilogue = 2;
+    }
     if (M > 64 || K < 32 || K % 32 != 0 || lda % 8 != 0 || ldw % 8 != 0) return kErrUnsupportedSize;
     if (((uintptr_t)A | (uintptr_t)W) & 15) return kErrUnsupportedSize;
     if (epilogue < 0 || epilogue > 2 || (epilogue == 1 && c_dtype != kF32) || (epilogue == 2 && (N & 1)))
@@ -310,7 +320,8 @@ static int gemm_decode_launch(const void* A, int lda, const void* W, int ldw, vo
 
 }  // namespace b200
 
-// A, W bfloat16; C bfloat16 or float32 (c_dtype); epilogue 0 store, 1 residual add (C float32), 2 gated SiLU.
+// A, W bfloat16; C bfloat16 or float32 (c_dtype); epilogue 0 store, 1 residual add (C float32), 2 gated SiLU,
+// 3 gated GELU (tanh form).
 extern "C" int b200_gemm_decode(const void* A, int lda, const void* W, int ldw, void* C, int c_dtype, int ldc, int M,
                                 int N, int K, int epilogue, cudaStream_t stream) {
     return b200::gemm_decode_launch(A, lda, W, ldw, C, c_dtype, ldc, M, N, K, epilogue, b200::NormLink{}, stream);

@@ -11,21 +11,14 @@ import torch
 from . import ops
 
 
-def gemm_has_epilogue(a, w: torch.Tensor, epilogue: int) -> bool:
-    """Whether the kernel that will multiply ``a`` with ``w`` applies ``epilogue`` itself.  The plain kernel has all
-    of them; the tensor-core kernels of the bfloat16 run have the store, the residual sum and the gated SiLU."""
-    if getattr(a, "dtype", None) != torch.bfloat16 or w.dtype != torch.bfloat16:
-        return True
-    return epilogue != ops.EPILOGUE_GATED_GELU_TANH
-
-
 def try_gemm(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int) -> bool:
-    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or epilogue == ops.EPILOGUE_GATED_GELU_TANH:
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         return False
     M = a.shape[0]
     if M <= 16:
         return ops.gemm_decode(a, w, c, epilogue)
-    if M <= 128 and ops.gemm_skinny(a, w, c, epilogue):
+    # (the few-token tensor-core kernel has the gated epilogue with SiLU only; with GELU those sizes go to the other two)
+    if M <= 128 and epilogue != ops.EPILOGUE_GATED_GELU_TANH and ops.gemm_skinny(a, w, c, epilogue):
         return True
     if M <= 64 and ops.gemm_decode(a, w, c, epilogue):
         return True

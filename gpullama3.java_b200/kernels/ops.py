@@ -79,7 +79,6 @@ _SIGNATURES = {
     "b200_head_rows": ("head_rows", [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                      c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
     "b200_softcap_rows": ("elementwise", [c_void_p, ctypes.c_longlong, c_float]),
-    "b200_gated_activation": ("elementwise", [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int]),
     "b200_gated_rmsnorm": ("elementwise", [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
                                            c_float]),
     "b200_causal_conv_silu": ("delta_rule", [c_void_p, c_int, c_void_p, c_void_p, ctypes.c_longlong, c_void_p, c_void_p,
@@ -266,7 +265,7 @@ def attention_paged(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, posit
 # --------------------------------------------------------------------------- matrix products
 EPILOGUE_STORE, EPILOGUE_RESIDUAL_ADD, EPILOGUE_GATED_SILU, EPILOGUE_GATED_GELU_TANH = 0, 1, 2, 3
 GATED_EPILOGUES = (EPILOGUE_GATED_SILU, EPILOGUE_GATED_GELU_TANH)
-ACTIVATION_CODES = {"silu": 0, "gelu_tanh": 1}   # elementwise.cu
+ACTIVATION_CODES = {"silu": 0, "gelu_tanh": 1}   # the gated epilogues' activations of the gate value
 
 
 def gemm_generic(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int = EPILOGUE_STORE) -> None:
@@ -305,7 +304,7 @@ def gemm_decode(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int
     _dev(a, w, c)
     N = w.shape[0]
     assert w.shape[1] == K and c.stride(1) == 1 and c.shape[0] == M
-    assert c.shape[1] == (N // 2 if epilogue == EPILOGUE_GATED_SILU else N)
+    assert c.shape[1] == (N // 2 if epilogue in GATED_EPILOGUES else N)
     _check(_fn("b200_gemm_decode")(a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), c.data_ptr(),
                                    dtype_code(c.dtype), c.stride(0), M, N, K, epilogue, _stream()), "gemm_decode")
     return True
@@ -337,7 +336,7 @@ def gemm_decode_linked(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilog
     _dev(a, w, c)
     assert a.dtype == torch.bfloat16 and gemm_decode_links(M, w) and a.stride(1) == 1 and a.stride(0) % 8 == 0
     assert w.shape[1] == K and c.stride(1) == 1 and c.shape[0] == M and a.data_ptr() % 16 == 0
-    assert c.shape[1] == (N // 2 if epilogue == EPILOGUE_GATED_SILU else N)
+    assert c.shape[1] == (N // 2 if epilogue in GATED_EPILOGUES else N)
     in_p, n_in, eps, dim = None, 0, 0.0, 0
     if row_factors is not None:
         part, eps, dim = row_factors
@@ -373,12 +372,12 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: in
     if (a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or K % 8 or K < 8 or a_inner != 1 or w_inner != 1
             or lda % 8 or ldw % 8 or (pa | pw) & 15):
         return False
-    if epilogue == EPILOGUE_GATED_SILU and c.dtype != torch.bfloat16:
+    if epilogue in GATED_EPILOGUES and c.dtype != torch.bfloat16:
         return False
     _dev(a, w, c)
     N, Kw = w.shape
     ldc, c_inner = c.stride()
-    assert Kw == K and c_inner == 1 and c.shape == (M, N // 2 if epilogue == EPILOGUE_GATED_SILU else N)
+    assert Kw == K and c_inner == 1 and c.shape == (M, N // 2 if epilogue in GATED_EPILOGUES else N)
     _check(_fn("b200_gemm_tcgen05")(pa, lda, pw, ldw, c.data_ptr(), dtype_code(c.dtype), ldc, M, N, K, epilogue,
                                     tile_width, k_spans, cta_pair, _stream()), "gemm_tcgen05")
     return True
@@ -446,12 +445,12 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int
     if (a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or M > 128 or K % 8 or K < 8 or a.stride(1) != 1
             or w.stride(1) != 1 or a.stride(0) % 8 or w.stride(0) % 8 or (a.data_ptr() | w.data_ptr()) & 15):
         return False
-    if epilogue == EPILOGUE_GATED_SILU and c.dtype != torch.bfloat16:
+    if epilogue == EPILOGUE_GATED_GELU_TANH or (epilogue == EPILOGUE_GATED_SILU and c.dtype != torch.bfloat16):
         return False
     _dev(a, w, c)
     N = w.shape[0]
     assert w.shape[1] == K and c.stride(1) == 1 and c.shape[0] == M
-    assert c.shape[1] == (N // 2 if epilogue == EPILOGUE_GATED_SILU else N)
+    assert c.shape[1] == (N // 2 if epilogue in GATED_EPILOGUES else N)
     fn = _fn("b200_gemm_skinny")
     if k_splits is None:
         k_splits = library("gemm_skinny_tcgen05").b200_gemm_skinny_splits(M, N, K, _sm_count(a.device))
@@ -762,16 +761,6 @@ def softcap_rows(logits: torch.Tensor, cap: float) -> None:
     _dev(logits)
     assert logits.dtype == torch.float32 and logits.is_contiguous()
     _check(_fn("b200_softcap_rows")(logits.data_ptr(), logits.numel(), float(cap), _stream()), "softcap_rows")
-
-
-def gated_activation(pairs: torch.Tensor, out: torch.Tensor, activation: int) -> None:
-    """out[t, j] = act(pairs[t, 2j]) * pairs[t, 2j + 1]."""
-    _dev(pairs, out)
-    assert pairs.dtype == out.dtype and pairs.stride(1) == 1 and out.stride(1) == 1
-    assert pairs.shape[0] == out.shape[0] and pairs.shape[1] == 2 * out.shape[1]
-    _check(_fn("b200_gated_activation")(pairs.data_ptr(), pairs.stride(0), out.data_ptr(), out.stride(0),
-                                        dtype_code(out.dtype), out.shape[0], out.shape[1], int(activation), _stream()),
-           "gated_activation")
 
 
 def gated_rmsnorm(x: torch.Tensor, weight: torch.Tensor, gate: torch.Tensor, out: torch.Tensor, n_heads: int, d: int,

@@ -26,6 +26,7 @@ from .linear import Linear
 class LatentAttention(Mixer):
     graph_safe = True
     pad_safe = True
+    DECODE_GROUP = 16   # query heads per key/value head that the decode attention kernel takes
 
     def __init__(self, hidden_size: int, n_heads: int, head_dim: int, value_dim: int, kv_rank: int, q_rank: int,
                  norm_eps: float, scale: float | None = None, window: int | None = None):
@@ -57,7 +58,7 @@ class LatentAttention(Mixer):
         capacity = ctx.capacity(cache.group)
         if self.window:
             capacity = min(capacity, self.window)
-        resident = ops.resident_ctas(ctx.device, self.head_dim, self.n_heads)
+        resident = ops.resident_ctas(ctx.device, self.head_dim, min(self.n_heads, self.DECODE_GROUP))
         splits = ops.attention_decode_splits(ctx.n_seqs, 1, capacity, resident)
         return splits, ops.attention_decode_early_start(ctx.n_seqs, 1, capacity, splits)
 
@@ -96,13 +97,24 @@ class LatentAttention(Mixer):
         q = self.uq.store(c_q[:, :self.q_rank], ctx.dtype, ctx.empty)         # [T, H dk]
         carried = ctx.empty((T, H * D), ctx.dtype)                            # queries in the latent space
         ops.gemm_per_head(q, self.carry_in, carried)
+        heads = ctx.empty((T, H * dv), ctx.dtype)
+        if ctx.all_decode and H > self.DECODE_GROUP and ops.attention_decode_supported(ctx.dtype, self.DECODE_GROUP, 1, D):
+            # the decode kernel takes up to DECODE_GROUP query heads per key/value head: the heads go in groups, each
+            # group over the same cached latents
+            splits, early = self.plan_decode(ctx, cache)
+            for g in range(0, H, self.DECODE_GROUP):
+                n = min(self.DECODE_GROUP, H - g)
+                part = ctx.empty((T, n * D), ctx.dtype)
+                ops.attention_decode(carried[:, g * D:], carried.stride(0), part, ctx.kv_lens, table, cache.k, cache.v, n, 1,
+                                     D, self.window or 0, splits, early_start=early)
+                ops.gemm_per_head(part, self.carry_out[g:g + n], heads[:, g * dv:(g + n) * dv])
+            return self.o.add_to(heads, residual, then_norm)
         out = ctx.empty((T, H * D), ctx.dtype)
         if not fast.try_attention(carried, out, ctx, table, cache, self):
             n_rows = T * H
             splits = 1 if n_rows >= 1024 else max(1, min(16, 1024 // n_rows, ctx.capacity(cache.group) // 512))
             ops.attention_paged(carried, carried.stride(0), out, ctx.positions, ctx.seq_ids, table, cache.k, cache.v,
                                 H, 1, D, self.window or 0, n_splits=splits)
-        heads = ctx.empty((T, H * dv), ctx.dtype)
         ops.gemm_per_head(out, self.carry_out, heads)
         return self.o.add_to(heads, residual, then_norm)
 

@@ -61,15 +61,8 @@ class Linear:
 
     def gated(self, a: torch.Tensor, out_dtype: torch.dtype, alloc=None, activation: str = "silu") -> torch.Tensor:
         """W holds gate and up rows interleaved; returns act(gate) * up as [T, out/2] (``activation``: ``silu`` or
-        ``gelu_tanh``).  The activation is applied in the product's epilogue where the chosen kernel has it, else by
-        a kernel of its own over the stored pairs."""
+        ``gelu_tanh``), the activation applied in the product's epilogue."""
         shape = (a.shape[0], self.out_features // 2)
         c = alloc(shape, out_dtype) if alloc is not None else torch.empty(shape, dtype=out_dtype, device=a.device)
-        epilogue = ops.EPILOGUE_GATED_SILU if activation == "silu" else ops.EPILOGUE_GATED_GELU_TANH
-        if isinstance(a, ScaledRows) or fast.gemm_has_epilogue(a, self.weight, epilogue):
-            self._run(a, c, epilogue)
-        else:
-            pairs = (alloc or (lambda sh, dt: torch.empty(sh, dtype=dt, device=a.device)))((a.shape[0], self.out_features), out_dtype)
-            self._run(a, pairs, ops.EPILOGUE_STORE)
-            ops.gated_activation(pairs, c, ops.ACTIVATION_CODES[activation])
+        self._run(a, c, ops.EPILOGUE_GATED_SILU if activation == "silu" else ops.EPILOGUE_GATED_GELU_TANH)
         return c

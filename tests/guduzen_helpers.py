@@ -4,7 +4,8 @@ The three configurations differ from one another in every size and option: numbe
 or none, layer order, heads and groups, key size against value size (smaller, equal, larger), sizes that the
 tensor-core kernels take (64, 128) and sizes that are widened (24 -> 32, 40 -> 64), windows shorter and longer than a
 page and none at all, a reader of another layer's cache with a longer window than the writer's own, convolutions of 2
-to 4 taps, delta heads that share query/key heads, layers without feed-forward.  Score scales are large, so attention
+to 4 taps, delta heads that share query/key heads, more latent-attention heads than one decode launch takes, layers without
+feed-forward.  Score scales are large, so attention
 is peaked and one key that is wrongly seen or missed moves the logits."""
 from __future__ import annotations
 
@@ -33,7 +34,7 @@ GUDUZEN_B = {
     "architecture": "Guduzen", "vocab": 200, "width": 96, "norm": {"eps": 1e-6}, "initializer_range": 0.06,
     "layers": [
         {"type": "latent_attention", "mlp": None,
-         "mixer": {"heads": 3, "dim": 32, "vdim": 16, "kv_rank": 64, "q_rank": 20, "scale": 0.6}},
+         "mixer": {"heads": 20, "dim": 32, "vdim": 16, "kv_rank": 64, "q_rank": 20, "scale": 0.6}},
         {"type": "attention", "mlp": {"kind": "dense", "ff": 128},
          "mixer": {"heads": 2, "kv_heads": 2, "dim": 128, "vdim": 128, "scale": 0.25}},
         {"type": "channel_delta", "mlp": {"kind": "dense", "ff": 64},

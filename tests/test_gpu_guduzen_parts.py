@@ -75,32 +75,29 @@ def test_head_rows(dtype):
     assert float(got[:, :H + G, dk:].abs().max()) == 0.0 and float(got[:, H + G:, dv:].abs().max()) == 0.0
 
 
-def test_softcap_and_gated_activation():
+def test_softcap():
     x = _rand(7, 300, seed=1, scale=30.0).cuda()
     ref = plain.softcap(x.cpu().to(F), 12.5)
     ops.softcap_rows(x, 12.5)
     torch.testing.assert_close(x.cpu().to(F), ref, rtol=1e-5, atol=1e-5)
-    pairs = _rand(5, 2 * 77, seed=2, scale=3.0).cuda()
-    out = torch.empty(5, 77, device="cuda")
-    ops.gated_activation(pairs, out, ops.ACTIVATION_CODES["gelu_tanh"])
-    p = pairs.cpu().to(F)
-    torch.testing.assert_close(out.cpu().to(F), plain.gelu_tanh(p[:, 0::2]) * p[:, 1::2], rtol=1e-5, atol=1e-5)
 
 
 @DTYPES
-@pytest.mark.parametrize("M", [3, 40, 300])
-def test_gated_gelu_feed_forward_product(dtype, M):
-    """The gate/up product with the GELU in its epilogue (plain kernel) or behind it (tensor-core kernels)."""
+@pytest.mark.parametrize("M, K, N", [(3, 64, 96), (12, 96, 40), (40, 64, 96), (100, 64, 96), (300, 64, 96), (700, 200, 520),
+                                     (2048, 512, 1536), (5, 60, 30)])
+def test_gated_gelu_feed_forward_product(dtype, M, K, N):
+    """The gate/up product with the GELU in its epilogue: the plain kernel, the decode kernel, the tensor-core kernels
+    for prompts (single CTAs and pairs), and sizes none of those takes."""
     from gpullama3.java_b200.parts.linear import Linear
 
-    K, N = 64, 96
     x = _rand(M, K, seed=1).to(dtype).cuda()
     gate, up = _rand(N, K, seed=2, scale=0.2).to(dtype), _rand(N, K, seed=3, scale=0.2).to(dtype)
     lin = Linear(torch.stack([gate, up], dim=1).reshape(2 * N, K).contiguous().cuda())
     out = lin.gated(x, dtype, None, "gelu_tanh")
     xf = x.cpu().to(F)
     ref = plain.gelu_tanh(xf @ gate.to(F).T) * (xf @ up.to(F).T)
-    torch.testing.assert_close(out.cpu().to(F), ref, **_tol(dtype))
+    tol = dict(rtol=1e-4, atol=1e-4) if dtype == torch.float32 else dict(rtol=3e-2, atol=3e-2)   # (sums of up to 512 products)
+    torch.testing.assert_close(out.cpu().to(F), ref, **tol)
 
 
 @DTYPES

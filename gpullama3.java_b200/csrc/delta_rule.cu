@@ -25,26 +25,69 @@ constexpr int kScanThreads = 128;
 constexpr int kChunk = 16;
 constexpr int kMaxTaps = 16;
 
-template <typename T>
+template <typename T, int VEC> struct ConvVec;
+template <typename T> struct ConvVec<T, 1> {
+    __device__ static void load(const T* p, float (&f)[1]) { f[0] = to_f32<T>(p[0]); }
+    __device__ static void store(T* p, const float (&f)[1]) { p[0] = from_f32<T>(f[0]); }
+};
+template <> struct ConvVec<float, 4> {
+    __device__ static void load(const float* p, float (&f)[4]) {
+        const float4 v = *reinterpret_cast<const float4*>(p);
+        f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+    }
+    __device__ static void store(float* p, const float (&f)[4]) { *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]); }
+};
+template <> struct ConvVec<__nv_bfloat16, 8> {
+    __device__ static void load(const __nv_bfloat16* p, float (&f)[8]) {
+        const uint4 v = *reinterpret_cast<const uint4*>(p);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            f[2 * i] = __uint_as_float(w[i] << 16);
+            f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+    }
+    __device__ static void store(__nv_bfloat16* p, const float (&f)[8]) {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+            w[i] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+};
+
+// A thread takes VEC neighbouring channels of one token (16 bytes per access when the sizes and pointers allow).
+template <typename T, int VEC>
 __global__ void causal_conv_silu_kernel(const T* __restrict__ x, int ld_x, const float* __restrict__ w,
                                         const float* __restrict__ state, size_t slot_stride, const int* __restrict__ slots,
                                         const int* __restrict__ seq_ids, const int* __restrict__ cu_seqlens,
                                         T* __restrict__ out, int ld_out, int channels, int taps) {
     const int t = blockIdx.y;
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
     if (c >= channels) return;
     const int seq = seq_ids[t];
     const int local = t - cu_seqlens[seq];
     const float* st = state + (size_t)slots[seq] * slot_stride;   // [taps - 1][channels], oldest first
-    float acc = 0.f;
+    float acc[VEC];
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) acc[e] = 0.f;
     for (int j = 0; j < taps; ++j) {
         const int back = taps - 1 - j;          // how many tokens before t
-        float v;
-        if (local - back >= 0) v = to_f32<T>(x[(size_t)(t - back) * ld_x + c]);
-        else v = st[(size_t)(taps - 1 + local - back) * channels + c];
-        acc += w[(size_t)c * taps + j] * v;
+        float v[VEC];
+        if (local - back >= 0) {
+            ConvVec<T, VEC>::load(x + (size_t)(t - back) * ld_x + c, v);
+        } else {
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) v[e] = st[(size_t)(taps - 1 + local - back) * channels + c + e];
+        }
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) acc[e] += w[(size_t)(c + e) * taps + j] * v[e];
     }
-    out[(size_t)t * ld_out + c] = from_f32<T>(acc / (1.0f + expf(-acc)));
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) acc[e] = acc[e] / (1.0f + expf(-acc[e]));
+    ConvVec<T, VEC>::store(out + (size_t)t * ld_out + c, acc);
 }
 
 template <typename T>
@@ -262,9 +305,19 @@ extern "C" int b200_causal_conv_silu(const void* x, int ld_x, const float* w, fl
     if (taps < 1 || taps > b200::kMaxTaps) return b200::kErrUnsupportedSize;
     if (n_tokens > 65535 || n_seqs > 65535) return b200::kErrUnsupportedSize;
     dim3 grid((channels + 127) / 128, n_tokens), grid_u((channels + 127) / 128, n_seqs);
+    const int vec = dtype == b200::kF32 ? 4 : 8;
+    const bool wide = channels % vec == 0 && ld_x % vec == 0 && ld_out % vec == 0 && (((uintptr_t)x | (uintptr_t)out) & 15) == 0;
+    const dim3 grid_v((channels / vec + 127) / 128, n_tokens);
+    if (dtype == b200::kF32 && wide)
+        b200::causal_conv_silu_kernel<float, 4><<<grid_v, 128, 0, stream>>>((const float*)x, ld_x, w, state, (size_t)slot_stride, slots,
+                                                                            seq_ids, cu_seqlens, (float*)out, ld_out, channels, taps);
+    else if (dtype == b200::kBF16 && wide)
+        b200::causal_conv_silu_kernel<__nv_bfloat16, 8><<<grid_v, 128, 0, stream>>>((const __nv_bfloat16*)x, ld_x, w, state, (size_t)slot_stride, slots,
+                                                                                    seq_ids, cu_seqlens, (__nv_bfloat16*)out, ld_out, channels, taps);
     B200_DISPATCH_DTYPE(dtype, T,
-        b200::causal_conv_silu_kernel<T><<<grid, 128, 0, stream>>>((const T*)x, ld_x, w, state, (size_t)slot_stride, slots,
-                                                                   seq_ids, cu_seqlens, (T*)out, ld_out, channels, taps);
+        if (!wide)
+            b200::causal_conv_silu_kernel<T, 1><<<grid, 128, 0, stream>>>((const T*)x, ld_x, w, state, (size_t)slot_stride, slots,
+                                                                          seq_ids, cu_seqlens, (T*)out, ld_out, channels, taps);
         if (update_state && taps > 1)
             b200::conv_state_update_kernel<T><<<grid_u, 128, 0, stream>>>((const T*)x, ld_x, state, (size_t)slot_stride, slots,
                                                                           cu_seqlens, channels, taps));

@@ -2,6 +2,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--model 1b|3b|8b] [--dtype bfloat16|float32]
                     [--batch 8] [--context 4096] [--layers L] [--sizes all|none]
+    python bench.py --design guduzen [--design-sizes s,m]     (another workload, see the end of this text)
 
 Default run: the Llama-3.2-1B shape (BASELINE.json configs[2]) with random bfloat16 weights, a
 batch of 8 sequences at context length 4096.  A "step" is one decode step.  ``value`` is decoded
@@ -18,6 +19,11 @@ the headline of the line instead.  One JSON line on stdout; everything else goes
 The reference counts prompt and generated tokens over the whole loop's wall time, load excluded
 (auxiliary/LastRunMetrics.java:20-32, inference/InferenceEngine.java:281,358-363 of the reference
 project); here the prompt step and the decode steps are timed apart, on the device.
+
+``--design guduzen`` leaves the default workload alone and times the Guduzen decoder instead (layers in the order window
+attention, attention reading that layer's cache, latent attention, delta rule; three residual streams) beside a Llama 3
+decoder of the same width, depth, heads and vocabulary at two sizes: a prompt of 2,048 tokens, decode steps at
+``--batch`` and a context of 2,048, and the device time of every kernel function in one prompt pass and one decode step.
 
 The library runs on one GPU: for --gpus N > 1 it says so and exits with 2.
 """

@@ -223,11 +223,20 @@ __device__ __forceinline__ void epilogue_tile(uint32_t acc, int quarter, int lan
             TC* dst = C + (size_t)row * ldc + (col >> 1);
             if (col + 32 <= N && ((uintptr_t)dst & 15) == 0 && sizeof(TC) == 2) {
                 uint32_t pk[8];
+                if (rope.gate_act == 0) {   // (one branch per 32 columns, not one choice per value)
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const float g0 = v[4 * j], u0 = v[4 * j + 1], g1 = v[4 * j + 2], u1 = v[4 * j + 3];
-                    __nv_bfloat162 h = __floats2bfloat162_rn(gated_pair(g0, u0, rope.gate_act), gated_pair(g1, u1, rope.gate_act));
-                    pk[j] = *reinterpret_cast<uint32_t*>(&h);
+                    for (int j = 0; j < 8; ++j) {
+                        const float g0 = v[4 * j], u0 = v[4 * j + 1], g1 = v[4 * j + 2], u1 = v[4 * j + 3];
+                        __nv_bfloat162 h = __floats2bfloat162_rn((g0 / (1.0f + expf(-g0))) * u0, (g1 / (1.0f + expf(-g1))) * u1);
+                        pk[j] = *reinterpret_cast<uint32_t*>(&h);
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const float g0 = v[4 * j], u0 = v[4 * j + 1], g1 = v[4 * j + 2], u1 = v[4 * j + 3];
+                        __nv_bfloat162 h = __floats2bfloat162_rn(gated_pair(g0, u0, 1), gated_pair(g1, u1, 1));
+                        pk[j] = *reinterpret_cast<uint32_t*>(&h);
+                    }
                 }
                 uint4* d = reinterpret_cast<uint4*>(dst);
                 d[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);

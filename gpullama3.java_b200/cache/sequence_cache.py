@@ -13,7 +13,7 @@ sequence (inference/state/LlamaState.java:44-46,61-64 of the reference project).
   one page table per sequence (shared by the group's entries).  ``KVGroup`` is the paged group of
   attention: keys ``[entry][page][kv_head][64][head_dim]``, values transposed
   ``[entry][page][kv_head][head_dim][64]``; with a ``window`` it only keeps the pages a query can
-  still reach;
+  still reach (and the pages of the first ``keep_first`` positions, if the need has any);
 * a *slot group* has a fixed size per sequence: ``StateGroup`` owns ``[entry][slot][...shape]``,
   zeroed when a slot is acquired;
 * a *slot* is acquired when a sequence starts and released when it ends; its pages go back to
@@ -32,10 +32,12 @@ from .pages import PAGE_TOKENS, CacheError, CacheFull, PagePool, SlotTable, page
 @dataclass(frozen=True)
 class KVCacheNeed:
     """Growing keys and values: one [kv_heads, head_dim] row per position; ``window`` = how many
-    of the latest positions a query reads (None: all of them)."""
+    of the latest positions a query reads (None: all of them); with a window, the first ``keep_first``
+    positions of a sequence stay readable for good."""
     n_kv_heads: int
     head_dim: int
     window: int | None = None
+    keep_first: int = 0
 
 
 @dataclass(frozen=True)
@@ -87,12 +89,13 @@ class PagedGroup(CacheGroup):
     """Bookkeeping of a group that grows page by page; subclasses own the device storage and the view."""
     paged = True
 
-    def __init__(self, need, entries, sizes: CacheSizes, window: int | None = None):
+    def __init__(self, need, entries, sizes: CacheSizes, window: int | None = None, keep_first: int = 0):
         super().__init__(need, entries, sizes)
         self.window = window
+        self.kept_pages = pages_for(keep_first) if window is not None else 0   # a sequence's first pages that are never let go
         n_pages = sizes.n_pages
         if window is not None:   # a windowed group never holds more than this, whatever the promised total
-            per_seq = pages_for(window + max(sizes.window_slack, 1)) + 1
+            per_seq = pages_for(window + max(sizes.window_slack, 1)) + 1 + self.kept_pages
             n_pages = min(n_pages, sizes.max_slots * per_seq)
         self.pool = PagePool(n_pages)
         # per live slot: logical page index -> physical page, -1 where a windowed group let go
@@ -119,10 +122,10 @@ class PagedGroup(CacheGroup):
         first_needed = max(0, new_length - self.window + 1)  # the next query sits at position `new_length`
         dead = first_needed // PAGE_TOKENS
         row = self.rows[slot]
-        drop = [p for p in row[:dead] if p >= 0]
+        drop = [p for p in row[self.kept_pages:dead] if p >= 0]
         if drop:
             self.pool.free(drop)
-            for i in range(dead):
+            for i in range(self.kept_pages, dead):
                 row[i] = -1
 
     def check(self):
@@ -145,7 +148,7 @@ class KVView:
 
 class KVGroup(PagedGroup):
     def __init__(self, need: KVCacheNeed, entries, sizes: CacheSizes):
-        super().__init__(need, entries, sizes, window=need.window)
+        super().__init__(need, entries, sizes, window=need.window, keep_first=need.keep_first)
         n = self.pool.n_pages
         # keys: a row per position; values: transposed, a row per dimension (positions contiguous)
         self.k = torch.zeros((len(self.entries), n, need.n_kv_heads, PAGE_TOKENS, need.head_dim), dtype=sizes.dtype,

@@ -5,8 +5,9 @@ from .registry import (Architecture, architecture_of, config_from_dict, load_con
                        registered_architectures, unregister_architecture)
 from .llama import LlamaConfig, RopeScaling
 from .guduzen import GuduzenConfig
+from .pekerax import PekeraxConfig
 
 __all__ = ["ConfigError", "LayerSpec", "ModelConfig", "PartSpec", "ScheduleEntry", "default_schedule",
            "read_config_json", "Architecture", "architecture_of", "config_from_dict", "load_config",
            "register_architecture", "registered_architectures", "unregister_architecture", "LlamaConfig",
-           "RopeScaling", "GuduzenConfig"]
+           "RopeScaling", "GuduzenConfig", "PekeraxConfig"]

@@ -110,6 +110,10 @@ class ModelConfig:
         """Standard deviation of random matrices in the random-weights mode."""
         return 0.02
 
+    def embedding_scale(self) -> float:
+        """What the embedding rows are multiplied with as they enter the residual stream."""
+        return 1.0
+
     def output_softcap(self) -> float | None:
         """c when the logits leave the head as c * tanh(logits / c); None when they leave as they are."""
         return None

@@ -9,11 +9,28 @@
 //     out = sum_t p_t v_t                                        (:136-144)
 // Query head h reads kv head h / (n_heads / n_kv_heads).  The softmax is computed online over
 // tiles of 128 keys in 32-bit.  `window` > 0 keeps only the last `window` keys.
+//
+// Optional further terms (AttentionTerms; all off for the Llama 3 decoder):
+//   keep_first  with a window, the first keep_first positions of a sequence stay visible to every later query
+//               (position i sees j when j <= i and (i - j < window or j < keep_first)); the keys a query reads are
+//               then two runs, [0, min(keep_first, first)) and [first, i], walked as one row of tiles
+//   slopes      a distance penalty per query head: score -= slopes[h] * (i - j), in 32 bits
+//   sinks       a learned number per query head whose exponential joins the softmax's denominator (a key without
+//               a value): the running maximum and sum start at (sinks[h], 1) instead of (-inf, 0)
+//   gate        a number per (token, head), before its sigmoid: the head's output is multiplied by sigmoid(gate)
 #include "common.cuh"
 
 namespace b200 {
 
 constexpr int kAttnThreads = 128;
+
+struct AttentionTerms {
+    int keep_first;
+    const float* slopes;   // [n_heads] or null
+    const float* sinks;    // [n_heads] or null
+    const void* gate;      // [T][ld_gate] of the run's storage type, column h, or null
+    int ld_gate;
+};
 
 template <typename T> struct Vec16;  // 16-byte vector of storage type T
 template <> struct Vec16<float> {
@@ -48,7 +65,7 @@ attention_paged_kernel(const T* __restrict__ q, int q_row_stride, T* __restrict_
                        const int* __restrict__ positions, const int* __restrict__ seq_ids,
                        const int* __restrict__ page_table, int table_stride, const T* __restrict__ k_pool,
                        const T* __restrict__ v_pool, int n_heads, int n_kv_heads, int head_dim, int window,
-                       float* __restrict__ part_o, float* __restrict__ part_ml) {
+                       float* __restrict__ part_o, float* __restrict__ part_ml, AttentionTerms terms) {
     constexpr int E = Vec16<T>::kElems;     // elements per 16-byte load
     extern __shared__ float smem[];
     float* q_s = smem;                      // [head_dim]
@@ -65,9 +82,13 @@ attention_paged_kernel(const T* __restrict__ q, int q_row_stride, T* __restrict_
     // unnormalised partial results (maximum, sum, output) for attention_paged_merge_kernel: a decode step has few
     // (token, head) pairs and long rows of keys.
     const int n_splits = gridDim.z, split = blockIdx.z;
-    const int tiles = (pos - first) / kAttnThreads + 1, per_split = (tiles + n_splits - 1) / n_splits;
-    const int lo = first + split * per_split * kAttnThreads;
-    const int last = min(pos, lo + per_split * kAttnThreads - 1);   // (lo > last: an empty span)
+    // the keys of this query, numbered 0 .. n_keys - 1: the kept first positions the window no longer covers, then the
+    // window; key number i is position i (i < n_keep) or first + i - n_keep
+    const int n_keep = min(terms.keep_first, first), n_keys = n_keep + pos - first + 1, shift = first - n_keep;
+    const int tiles = (n_keys - 1) / kAttnThreads + 1, per_split = (tiles + n_splits - 1) / n_splits;
+    const int lo = split * per_split * kAttnThreads;
+    const int last = min(n_keys - 1, lo + per_split * kAttnThreads - 1);   // (lo > last: an empty span)
+    const float slope = terms.slopes ? terms.slopes[h] : 0.f;
     const size_t page_stride = (size_t)n_kv_heads * kPageTokens * head_dim;
     const size_t head_off = (size_t)g * kPageTokens * head_dim;
     const int dim_blocks = (head_dim + 31) / 32;     // at most 8
@@ -80,6 +101,10 @@ attention_paged_kernel(const T* __restrict__ q, int q_row_stride, T* __restrict_
 #pragma unroll
     for (int b = 0; b < 8; ++b) acc[b] = 0.f;
     float m_run = -INFINITY, l_run = 0.f;
+    if (terms.sinks && split == 0) {
+        m_run = terms.sinks[h];
+        l_run = 1.f;
+    }
     const float sqrt_d = sqrtf((float)head_dim);
     const int sub = lane & 3;                // which quarter of a key's 16-byte pieces this lane reads
     const int vecs = head_dim / E;           // 16-byte pieces per key row
@@ -92,8 +117,9 @@ attention_paged_kernel(const T* __restrict__ q, int q_row_stride, T* __restrict_
             const int key = wbase + k8 + (lane >> 2);
             float dot = 0.f;
             if (key <= last) {
-                const T* kr = k_pool + (size_t)pages[key / kPageTokens] * page_stride + head_off +
-                              (size_t)(key % kPageTokens) * head_dim;
+                const int j = key < n_keep ? key : key + shift;
+                const T* kr = k_pool + (size_t)pages[j / kPageTokens] * page_stride + head_off +
+                              (size_t)(j % kPageTokens) * head_dim;
                 for (int v = sub; v < vecs; v += 4) {
                     float f[E];
                     Vec16<T>::load(kr + v * E, f);
@@ -107,7 +133,8 @@ attention_paged_kernel(const T* __restrict__ q, int q_row_stride, T* __restrict_
         }
         __syncwarp();
         const int key = base + tid;          // from here on a thread is a key
-        const float s = key <= last ? s_s[tid] / sqrt_d : -INFINITY;
+        const int j = key < n_keep ? key : key + shift;   // the key's position
+        const float s = key <= last ? s_s[tid] / sqrt_d - slope * (float)(pos - j) : -INFINITY;
         const float m_tile = block_max(s, red);
         const float m_new = fmaxf(m_run, m_tile);
         const float p = key <= last ? expf(s - m_new) : 0.f;
@@ -118,7 +145,7 @@ attention_paged_kernel(const T* __restrict__ q, int q_row_stride, T* __restrict_
         // ---- this warp's 32 keys times their values, 32 dimensions at a time
         const bool any = wbase <= last;       // (uniform in the warp)
         const T* vr = nullptr;
-        if (key <= last) vr = v_pool + (size_t)pages[key / kPageTokens] * page_stride + head_off + (key % kPageTokens);
+        if (key <= last) vr = v_pool + (size_t)pages[j / kPageTokens] * page_stride + head_off + (j % kPageTokens);
 #pragma unroll
         for (int b = 0; b < 8; ++b) {
             if (b >= dim_blocks) break;
@@ -152,10 +179,12 @@ attention_paged_kernel(const T* __restrict__ q, int q_row_stride, T* __restrict_
     __syncthreads();
     T* o = out + ((size_t)t * n_heads + h) * head_dim;
     const size_t row = ((size_t)t * n_heads + h) * n_splits + split;
+    float gate = 1.f;
+    if (terms.gate && n_splits == 1) gate = 1.0f / (1.0f + expf(-to_f32<T>(((const T*)terms.gate)[(size_t)t * terms.ld_gate + h])));
     for (int d = tid; d < head_dim; d += kAttnThreads) {
         float a = 0.f;
         for (int w = 0; w < kAttnThreads / 32; ++w) a += part[w * dim_blocks * 32 + d];
-        if (n_splits == 1) o[d] = from_f32<T>(a / l_run);
+        if (n_splits == 1) o[d] = from_f32<T>(a / l_run * gate);
         else part_o[row * head_dim + d] = a;
     }
     if (n_splits > 1 && tid == 0) {
@@ -167,8 +196,10 @@ attention_paged_kernel(const T* __restrict__ q, int q_row_stride, T* __restrict_
 // out[row] = sum_s o_s exp(m_s - m) / sum_s l_s exp(m_s - m) over the spans of a (token, head) row, in span order
 template <typename T>
 __global__ void attention_paged_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                             T* __restrict__ out, int n_splits, int head_dim) {
+                                             T* __restrict__ out, int n_splits, int head_dim, int n_heads,
+                                             const T* __restrict__ gate, int ld_gate) {
     const size_t row = blockIdx.x;
+    const float gv = gate ? 1.0f / (1.0f + expf(-to_f32<T>(gate[(row / n_heads) * ld_gate + row % n_heads]))) : 1.f;
     const float* ml = part_ml + row * n_splits * 2;
     float m = -INFINITY;
     for (int s = 0; s < n_splits; ++s) m = fmaxf(m, ml[2 * s]);
@@ -179,7 +210,7 @@ __global__ void attention_paged_merge_kernel(const float* __restrict__ part_o, c
             l += ml[2 * s + 1] * f;
             acc += part_o[(row * n_splits + s) * head_dim + d] * f;
         }
-        out[row * head_dim + d] = from_f32<T>(acc / l);
+        out[row * head_dim + d] = from_f32<T>(acc / l * gv);
     }
 }
 
@@ -190,8 +221,11 @@ __global__ void attention_paged_merge_kernel(const float* __restrict__ part_o, c
 extern "C" int b200_attention_paged(const void* q, int q_row_stride, void* out, int dtype, const int* positions,
                                     const int* seq_ids, const int* page_table, int table_stride, const void* k_pool,
                                     const void* v_pool, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
-                                    int window, int n_splits, float* scratch, cudaStream_t stream) {
+                                    int window, int n_splits, float* scratch, int keep_first, const float* slopes,
+                                    const float* sinks, const void* gate, int ld_gate, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
+    if (keep_first < 0 || (keep_first > 0 && window <= 0)) return b200::kErrBadArgument;
+    const b200::AttentionTerms terms = {keep_first, slopes, sinks, gate, ld_gate};
     if (n_splits < 1 || n_splits > 64 || (n_splits > 1 && scratch == nullptr)) return b200::kErrBadArgument;
     if (head_dim % 16 != 0 || head_dim < 16 || head_dim > 256) return b200::kErrUnsupportedSize;
     if (n_kv_heads <= 0 || n_heads % n_kv_heads != 0) return b200::kErrBadArgument;
@@ -202,8 +236,9 @@ extern "C" int b200_attention_paged(const void* q, int q_row_stride, void* out, 
     B200_DISPATCH_DTYPE(dtype, T,
         b200::attention_paged_kernel<T><<<grid, b200::kAttnThreads, smem, stream>>>(
             (const T*)q, q_row_stride, (T*)out, positions, seq_ids, page_table, table_stride, (const T*)k_pool,
-            (const T*)v_pool, n_heads, n_kv_heads, head_dim, window, part_o, part_ml);
+            (const T*)v_pool, n_heads, n_kv_heads, head_dim, window, part_o, part_ml, terms);
         if (n_splits > 1)
-            b200::attention_paged_merge_kernel<T><<<n_tokens * n_heads, 64, 0, stream>>>(part_o, part_ml, (T*)out, n_splits, head_dim));
+            b200::attention_paged_merge_kernel<T><<<n_tokens * n_heads, 64, 0, stream>>>(part_o, part_ml, (T*)out, n_splits, head_dim,
+                                                                                         n_heads, (const T*)gate, ld_gate));
     return b200::launch_status();
 }

@@ -1,4 +1,5 @@
-// The gated delta rule with one decay per key channel, and the short causal convolution in front of it.
+// The gated delta rule with one decay per key channel (or one per head, which is the same rule with all channels of a
+// head decaying alike), and the short causal convolution in front of it.
 //
 // Per sequence and head the mixer keeps a matrix S [d_k, d_v] of 32-bit numbers.  A token with unit-length
 // query q and key k [d_k], value v [d_v], write strength beta and per-channel decay g [d_k] in (0, 1) does
@@ -130,6 +131,7 @@ struct PrepareArgs {
     float* rows;            // [heads, T, row]
     int n_tokens, heads, kv_heads, d_k, d_v, d_pad, row;
     float q_scale, unit_eps;
+    int decay_per_head;     // 1: one decay per head (decay column h, dt_bias[h]) in place of one per key channel
 };
 
 __device__ __forceinline__ float softplus(float x) { return x > 20.f ? x : log1pf(expf(x)); }
@@ -145,7 +147,7 @@ delta_rule_prepare_kernel(PrepareArgs a) {
     const T* qr = (const T*)a.qkv + t * a.ld_qkv + (size_t)kvh * a.d_k;
     const T* kr = qr + (size_t)a.kv_heads * a.d_k;
     const T* vr = (const T*)a.qkv + t * a.ld_qkv + 2 * (size_t)a.kv_heads * a.d_k + (size_t)h * a.d_v;
-    const T* dr = (const T*)a.decay + t * a.ld_decay + (size_t)h * a.d_k;
+    const T* dr = (const T*)a.decay + t * a.ld_decay + (a.decay_per_head ? (size_t)h : (size_t)h * a.d_k);
     float* out = a.rows + ((size_t)h * a.n_tokens + t) * a.row;
     float sq = 0.f, sk = 0.f, qk = 0.f;
     for (int i = lane; i < a.d_k; i += 32) {
@@ -159,11 +161,13 @@ delta_rule_prepare_kernel(PrepareArgs a) {
     qk = warp_sum(qk);
     const float fq = a.q_scale / sqrtf(sq + a.unit_eps), fk = 1.0f / sqrtf(sk + a.unit_eps);
     const float neg_rate = -expf(a.a_log[h]);
+    const float g_head = a.decay_per_head ? expf(neg_rate * softplus(to_f32<T>(dr[0]) + a.dt_bias[h])) : 0.f;
     for (int i = lane; i < a.d_pad; i += 32) {
         const bool in = i < a.d_k;
         out[i] = in ? to_f32<T>(qr[i]) * fq : 0.f;
         out[a.d_pad + i] = in ? to_f32<T>(kr[i]) * fk : 0.f;
-        out[2 * a.d_pad + i] = in ? expf(neg_rate * softplus(to_f32<T>(dr[i]) + a.dt_bias[(size_t)h * a.d_k + i])) : 0.f;
+        out[2 * a.d_pad + i] = !in ? 0.f : a.decay_per_head ? g_head
+                                         : expf(neg_rate * softplus(to_f32<T>(dr[i]) + a.dt_bias[(size_t)h * a.d_k + i]));
     }
     for (int j = lane; j < a.d_v; j += 32) out[3 * a.d_pad + j] = to_f32<T>(vr[j]);
     if (lane == 0) {
@@ -355,7 +359,7 @@ extern "C" int b200_delta_rule_scan(const void* qkv, int ld_qkv, const void* bet
                                     int ld_decay, const float* dt_bias, const float* a_log, float* state,
                                     long long slot_stride, const int* slots, const int* cu_seqlens, float* out,
                                     float* scratch, int dtype, int n_tokens, int n_seqs, int heads, int kv_heads, int d_k,
-                                    int d_v, float q_scale, float unit_eps, cudaStream_t stream) {
+                                    int d_v, float q_scale, float unit_eps, int decay_per_head, cudaStream_t stream) {
     if (n_seqs <= 0 || n_tokens <= 0) return 0;
     if (heads < 1 || kv_heads < 1 || heads % kv_heads || d_k < 1 || d_v < 1 || n_seqs > 65535 || heads > 65535 || !scratch)
         return b200::kErrBadArgument;
@@ -364,7 +368,7 @@ extern "C" int b200_delta_rule_scan(const void* qkv, int ld_qkv, const void* bet
     const int row = b200_delta_rule_row(d_k, d_v);
     if ((uintptr_t)scratch % 16) return b200::kErrBadArgument;
     b200::PrepareArgs p = {qkv, ld_qkv, beta, ld_beta, decay, ld_decay, dt_bias, a_log, scratch, n_tokens, heads, kv_heads,
-                           d_k, d_v, rpt * lanes, row, q_scale, unit_eps};
+                           d_k, d_v, rpt * lanes, row, q_scale, unit_eps, decay_per_head ? 1 : 0};
     const long long units = (long long)n_tokens * heads;
     B200_DISPATCH_DTYPE(dtype, T,
         b200::delta_rule_prepare_kernel<T><<<(unsigned)((units + 3) / 4), 128, 0, stream>>>(p));

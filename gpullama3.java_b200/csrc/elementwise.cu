@@ -1,6 +1,6 @@
 // Small per-element and per-row kernels that several parts share.
 //   softcap_rows       x <- cap * tanh(x / cap), in place on 32-bit logits
-//   gated_rmsnorm      out[t, h, :] = x[t, h, :] / sqrt(mean(x^2) + eps) * w * sigmoid(gate[t, h, :])
+//   gated_rmsnorm      out[t, h, :] = x[t, h, :] / sqrt(mean(x^2) + eps) * w * act(gate[t, h, :]), act sigmoid or SiLU
 //                      per (token, head) row of 32-bit numbers: the output norm of a recurrent mixer
 #include "common.cuh"
 
@@ -15,7 +15,7 @@ __global__ void softcap_kernel(float* __restrict__ x, size_t n, float cap) {
 template <typename T>
 __global__ void __launch_bounds__(128)
 gated_rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, const T* __restrict__ gate, int ld_gate,
-                     T* __restrict__ out, int n_heads, int d, int n_rows, float eps) {
+                     T* __restrict__ out, int n_heads, int d, int n_rows, float eps, int gate_act) {
     const int row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (row >= n_rows) return;
     const int t = row / n_heads, h = row % n_heads;
@@ -28,7 +28,8 @@ gated_rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, c
     T* o = out + (size_t)row * d;
     for (int e = lane; e < d; e += 32) {
         const float z = to_f32<T>(g[e]);
-        o[e] = from_f32<T>(xr[e] * scale * w[e] * (1.0f / (1.0f + expf(-z))));
+        const float sig = 1.0f / (1.0f + expf(-z));
+        o[e] = from_f32<T>(xr[e] * scale * w[e] * (gate_act == 1 ? z * sig : sig));
     }
 }
 
@@ -43,12 +44,13 @@ extern "C" int b200_softcap_rows(float* x, long long n, float cap, cudaStream_t 
 }
 
 extern "C" int b200_gated_rmsnorm(const float* x, const float* w, const void* gate, int ld_gate, void* out, int dtype,
-                                  int n_tokens, int n_heads, int d, float eps, cudaStream_t stream) {
+                                  int n_tokens, int n_heads, int d, float eps, int gate_act, cudaStream_t stream) {
+    if (gate_act != 0 && gate_act != 1) return b200::kErrBadArgument;   // 0 sigmoid, 1 SiLU
     if (n_tokens <= 0 || n_heads <= 0) return 0;
     if (d < 1) return b200::kErrBadArgument;
     const long long rows = (long long)n_tokens * n_heads;
     B200_DISPATCH_DTYPE(dtype, T,
         b200::gated_rmsnorm_kernel<T><<<(int)((rows + 3) / 4), 128, 0, stream>>>(x, w, (const T*)gate, ld_gate, (T*)out,
-                                                                                 n_heads, d, (int)rows, eps));
+                                                                                 n_heads, d, (int)rows, eps, gate_act));
     return b200::launch_status();
 }

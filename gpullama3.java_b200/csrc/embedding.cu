@@ -1,4 +1,5 @@
-// Token embedding: x[t, :] = table[tokens[t], :], written to the 32-bit residual stream.
+// Token embedding: x[t, :] = scale * table[tokens[t], :], written to the 32-bit residual stream (the product with
+// `scale`, 1 for most models, is formed in 32 bits).
 // Restates the row copy of inference/InferenceCore.java:69 (reference project path) for a packed
 // batch of tokens on the device.
 #include "common.cuh"
@@ -7,7 +8,7 @@ namespace b200 {
 
 template <typename TW>
 __global__ void embed_gather_kernel(const TW* __restrict__ table, const int* __restrict__ tokens,
-                                    float* __restrict__ out, int dim, int vocab) {
+                                    float* __restrict__ out, int dim, int vocab, float scale) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
@@ -18,16 +19,16 @@ __global__ void embed_gather_kernel(const TW* __restrict__ table, const int* __r
         return;
     }
     const TW* row = table + (size_t)tok * dim;
-    for (int i = threadIdx.x; i < dim; i += blockDim.x) o[i] = to_f32<TW>(row[i]);
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) o[i] = to_f32<TW>(row[i]) * scale;
 }
 
 }  // namespace b200
 
 extern "C" int b200_embed_gather(const void* table, int table_dtype, const int* tokens, float* out,
-                                 int n_tokens, int dim, int vocab, cudaStream_t stream) {
+                                 int n_tokens, int dim, int vocab, float scale, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     B200_DISPATCH_DTYPE(table_dtype, TW,
         return b200::launch_pdl(b200::embed_gather_kernel<TW>, dim3(n_tokens), dim3(256), 0, stream, (const TW*)table,
-                                tokens, out, dim, vocab));
+                                tokens, out, dim, vocab, scale));
     return b200::launch_status();
 }

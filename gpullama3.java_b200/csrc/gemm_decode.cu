@@ -59,8 +59,10 @@ struct NormLink {
     __nv_bfloat16* out_act;     // [M][ld_out_act]
     int ld_out_act;
     float* out_partials;        // [M][gridDim.x]
-    // the gated epilogue's activation of the gate value: 0 SiLU, 1 GELU in its tanh form
+    // the gated epilogue's activation of the gate value: 0 SiLU, 1 GELU in its tanh form, 2 the clamped form
+    // min(g, limit) sigmoid(slope min(g, limit)) (clamp(u, -limit, limit) + 1)
     int gate_act;
+    float gate_limit, gate_slope;
 };
 
 // LINK: the product is a half of a split norm (the plain product is compiled without any of that)
@@ -220,8 +222,12 @@ gemm_decode_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bflo
         for (int idx = threadIdx.x; idx < NT * 8 * (ROWS / 2); idx += kDecodeThreads) {
             const int token = idx / (ROWS / 2), pair = idx % (ROWS / 2);
             if (token < M && row0 + 2 * pair + 1 < N) {
-                const float gate = fin[token][2 * pair], up = fin[token][2 * pair + 1];
-                const float act = link.gate_act == 1
+                float gate = fin[token][2 * pair], up = fin[token][2 * pair + 1];
+                if (link.gate_act == 2) {
+                    gate = fminf(gate, link.gate_limit);
+                    up = fminf(fmaxf(up, -link.gate_limit), link.gate_limit) + 1.0f;
+                }
+                const float act = link.gate_act == 2 ? gate / (1.0f + expf(-link.gate_slope * gate)) : link.gate_act == 1
                                       ? 0.5f * gate * (1.0f + tanhf(0.7978845608028654f * (gate + 0.044715f * gate * gate * gate)))
                                       : gate / (1.0f + expf(-gate));
                 C[(size_t)token * ldc + (row0 >> 1) + pair] = from_f32<TC>(act * up);
@@ -296,8 +302,8 @@ static int gemm_decode_launch(const void* A, int lda, const void* W, int ldw, vo
                               int K, int epilogue, const NormLink& link_in, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     NormLink link = link_in;
-    if (epilogue == 3) {   // the gated epilogue with the other activation
-        link.gate_act = 1;
+    if (epilogue == 3 || epilogue == 4) {   // the gated epilogue with another activation
+        link.gate_act = epilogue - 2;
         epilogue = 2;
     }
     if (M > 64 || K < 32 || K % 32 != 0 || lda % 8 != 0 || ldw % 8 != 0) return kErrUnsupportedSize;
@@ -321,10 +327,13 @@ static int gemm_decode_launch(const void* A, int lda, const void* W, int ldw, vo
 }  // namespace b200
 
 // A, W bfloat16; C bfloat16 or float32 (c_dtype); epilogue 0 store, 1 residual add (C float32), 2 gated SiLU,
-// 3 gated GELU (tanh form).
+// 3 gated GELU (tanh form), 4 gated and clamped (gate_limit, gate_slope).
 extern "C" int b200_gemm_decode(const void* A, int lda, const void* W, int ldw, void* C, int c_dtype, int ldc, int M,
-                                int N, int K, int epilogue, cudaStream_t stream) {
-    return b200::gemm_decode_launch(A, lda, W, ldw, C, c_dtype, ldc, M, N, K, epilogue, b200::NormLink{}, stream);
+                                int N, int K, int epilogue, float gate_limit, float gate_slope, cudaStream_t stream) {
+    b200::NormLink link{};
+    link.gate_limit = gate_limit;
+    link.gate_slope = gate_slope;
+    return b200::gemm_decode_launch(A, lda, W, ldw, C, c_dtype, ldc, M, N, K, epilogue, link, stream);
 }
 
 // How many CTAs, hence partial sums per row, the product (M, N) runs with.

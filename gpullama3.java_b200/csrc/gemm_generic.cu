@@ -11,20 +11,27 @@
 //   2  gated SiLU    C[M, N/2] = silu(acc[2j]) * acc[2j+1]   (W holds gate and up rows interleaved;
 //                    silu(g) = g / (1 + exp(-g)), inference/InferenceCore.java:163-166)
 //   3  gated GELU    the same with gelu(g) = 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))), the tanh form
+//   4  gated, clamped  with g = min(acc[2j], limit), u = clamp(acc[2j+1], -limit, limit):
+//                    C[M, N/2] = g sigmoid(slope g) (u + 1); limit and slope are arguments
 #include "common.cuh"
 
 namespace b200 {
 
 // the gated epilogues: activation of the gate value times the up value
-__device__ __forceinline__ float gated_pair(float gate, float up, int epilogue) {
+__device__ __forceinline__ float gated_pair(float gate, float up, int epilogue, float limit, float slope) {
+    if (epilogue == 4) {
+        const float g = fminf(gate, limit), u = fminf(fmaxf(up, -limit), limit);
+        return g / (1.0f + expf(-slope * g)) * (u + 1.0f);
+    }
     if (epilogue == 3) return 0.5f * gate * (1.0f + tanhf(0.7978845608028654f * (gate + 0.044715f * gate * gate * gate))) * up;
     return (gate / (1.0f + expf(-gate))) * up;
 }
 
 // Several products of one shape side by side (gridDim.z of them): product z reads A + z a, W + z w and writes C + z c
 // (elements).  One head's small product after another, for mixers that carry every head through a matrix of its own.
-struct BatchStrides {
+struct ProductExtras {
     long long a, w, c;
+    float gate_limit, gate_slope;   // epilogue 4 alone reads these
 };
 
 constexpr int kTileM = 64, kTileN = 64, kTileK = 16, kGemmThreads = 256;
@@ -32,7 +39,7 @@ constexpr int kTileM = 64, kTileN = 64, kTileK = 16, kGemmThreads = 256;
 template <typename TA, typename TW, typename TC>
 __global__ void __launch_bounds__(kGemmThreads)
 gemm_generic_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ W, int ldw, TC* __restrict__ C, int ldc,
-                    int M, int N, int K, int epilogue, BatchStrides batch) {
+                    int M, int N, int K, int epilogue, ProductExtras batch) {
     A += (size_t)blockIdx.z * batch.a;
     W += (size_t)blockIdx.z * batch.w;
     C += (size_t)blockIdx.z * batch.c;
@@ -77,7 +84,7 @@ gemm_generic_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ W,
                 const int n = n0 + tx * 4 + j;
                 if (n + 1 < N) {
                     const float gate = acc[i][j], up = acc[i][j + 1];
-                    C[(size_t)m * ldc + n / 2] = from_f32<TC>(gated_pair(gate, up, epilogue));
+                    C[(size_t)m * ldc + n / 2] = from_f32<TC>(gated_pair(gate, up, epilogue, batch.gate_limit, batch.gate_slope));
                 }
             }
         } else {
@@ -102,7 +109,7 @@ constexpr int kBigM = 128, kBigN = 128, kBigK = 16, kBigThreads = 256;
 template <typename TA, typename TW, typename TC>
 __global__ void __launch_bounds__(kBigThreads)
 gemm_generic_big_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ W, int ldw, TC* __restrict__ C, int ldc,
-                        int M, int N, int K, int epilogue, BatchStrides batch) {
+                        int M, int N, int K, int epilogue, ProductExtras batch) {
     A += (size_t)blockIdx.z * batch.a;
     W += (size_t)blockIdx.z * batch.w;
     C += (size_t)blockIdx.z * batch.c;
@@ -154,7 +161,7 @@ gemm_generic_big_kernel(const TA* __restrict__ A, int lda, const TW* __restrict_
                 const int n = n0 + tx * 8 + j;
                 if (n + 1 < N) {
                     const float gate = acc[i][j], up = acc[i][j + 1];
-                    C[(size_t)m * ldc + n / 2] = from_f32<TC>(gated_pair(gate, up, epilogue));
+                    C[(size_t)m * ldc + n / 2] = from_f32<TC>(gated_pair(gate, up, epilogue, batch.gate_limit, batch.gate_slope));
                 }
             }
         } else {
@@ -207,7 +214,7 @@ __device__ __forceinline__ float reduce_by_halving(float (&v)[32], int lane) {
 template <typename TA, typename TW, typename TC, int MT>
 __global__ void __launch_bounds__(kFewThreads)
 gemm_fewrows_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ W, int ldw, TC* __restrict__ C, int ldc,
-                    int M, int N, int K, int epilogue, BatchStrides batch) {
+                    int M, int N, int K, int epilogue, ProductExtras batch) {
     A += (size_t)blockIdx.z * batch.a;
     W += (size_t)blockIdx.z * batch.w;
     C += (size_t)blockIdx.z * batch.c;
@@ -256,7 +263,7 @@ gemm_fewrows_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ W,
         if ((r & 1) == 0) {
 #pragma unroll
             for (int wp = 0; wp < kFewWarps; ++wp) up += part[wp][i + MT];
-            if (m < M && n + 1 < N) C[(size_t)m * ldc + n / 2] = from_f32<TC>(gated_pair(sum, up, epilogue));
+            if (m < M && n + 1 < N) C[(size_t)m * ldc + n / 2] = from_f32<TC>(gated_pair(sum, up, epilogue, batch.gate_limit, batch.gate_slope));
         }
     } else if (m < M && n < N) {
         TC* c = C + (size_t)m * ldc + n;
@@ -267,7 +274,7 @@ gemm_fewrows_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ W,
 
 template <typename TA, typename TW, typename TC>
 static int launch_fewrows(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N, int K, int epilogue,
-                          int n_batch, BatchStrides batch, cudaStream_t stream) {
+                          int n_batch, ProductExtras batch, cudaStream_t stream) {
     const dim3 grid((N + kFewRows - 1) / kFewRows, 1, n_batch);
     if (M <= 8)
         gemm_fewrows_kernel<TA, TW, TC, 8><<<grid, kFewThreads, 0, stream>>>((const TA*)A, lda, (const TW*)W, ldw, (TC*)C, ldc, M, N, K, epilogue, batch);
@@ -280,10 +287,10 @@ static int launch_fewrows(const void* A, int lda, const void* W, int ldw, void* 
 
 static int gemm_generic_launch(const void* A, int a_dtype, int lda, const void* W, int w_dtype, int ldw, void* C,
                                int c_dtype, int ldc, int M, int N, int K, int epilogue, int n_batch,
-                               b200::BatchStrides batch, cudaStream_t stream) {
+                               b200::ProductExtras batch, cudaStream_t stream) {
     if (M <= 0 || N <= 0 || n_batch <= 0) return 0;
     if (n_batch > 65535) return b200::kErrUnsupportedSize;
-    if (K <= 0 || epilogue < 0 || epilogue > 3) return b200::kErrBadArgument;
+    if (K <= 0 || epilogue < 0 || epilogue > 4) return b200::kErrBadArgument;
     if (epilogue == 1 && c_dtype != b200::kF32) return b200::kErrBadArgument;
     if (epilogue >= 2 && (N & 1)) return b200::kErrBadArgument;
     // a decode step's few rows: rows of 4 elements at a time, when the rows start on such a boundary
@@ -308,8 +315,10 @@ static int gemm_generic_launch(const void* A, int a_dtype, int lda, const void* 
 }
 
 extern "C" int b200_gemm_generic(const void* A, int a_dtype, int lda, const void* W, int w_dtype, int ldw, void* C,
-                                 int c_dtype, int ldc, int M, int N, int K, int epilogue, cudaStream_t stream) {
-    return gemm_generic_launch(A, a_dtype, lda, W, w_dtype, ldw, C, c_dtype, ldc, M, N, K, epilogue, 1, b200::BatchStrides{0, 0, 0}, stream);
+                                 int c_dtype, int ldc, int M, int N, int K, int epilogue, float gate_limit,
+                                 float gate_slope, cudaStream_t stream) {
+    return gemm_generic_launch(A, a_dtype, lda, W, w_dtype, ldw, C, c_dtype, ldc, M, N, K, epilogue, 1,
+                               b200::ProductExtras{0, 0, 0, gate_limit, gate_slope}, stream);
 }
 
 // n_batch products of the same shape: product z uses A + z a_step, W + z w_step, C + z c_step (steps in elements).
@@ -317,5 +326,5 @@ extern "C" int b200_gemm_generic_batched(const void* A, int a_dtype, int lda, lo
                                          int ldw, long long w_step, void* C, int c_dtype, int ldc, long long c_step, int M,
                                          int N, int K, int n_batch, cudaStream_t stream) {
     return gemm_generic_launch(A, a_dtype, lda, W, w_dtype, ldw, C, c_dtype, ldc, M, N, K, 0, n_batch,
-                               b200::BatchStrides{a_step, w_step, c_step}, stream);
+                               b200::ProductExtras{a_step, w_step, c_step, 0.f, 0.f}, stream);
 }

@@ -84,8 +84,15 @@ struct RopeEpilogue {
     int n_heads, n_kv_heads, head_dim;
     int pairing;               // 0: (2j, 2j+1); 1: (j, j + head_dim/2)
     int write_cache;           // 0: keys and values are dropped (the layer reads a cache another layer writes)
-    int gate_act;              // the gated epilogue (EPI 2) alone reads this: 0 SiLU, 1 GELU in its tanh form, of the gate value
+    int gate_act;              // the gated epilogue (EPI 2) alone reads this: 0 SiLU, 1 GELU in its tanh form, of the gate value;
+                               // 2 the clamped form g' sigmoid(slope g') (u' + 1), g' = min(g, limit), u' = clamp(u, -limit, limit)
+    float gate_limit, gate_slope;
 };
+
+__device__ __forceinline__ float gated_clamped(float gate, float up, float limit, float slope) {
+    const float g = fminf(gate, limit), u = fminf(fmaxf(up, -limit), limit);
+    return g / (1.0f + expf(-slope * g)) * (u + 1.0f);
+}
 
 __device__ __forceinline__ float gated_pair(float gate, float up, int act) {
     if (act == 1) return 0.5f * gate * (1.0f + tanhf(0.7978845608028654f * (gate + 0.044715f * gate * gate * gate))) * up;
@@ -230,11 +237,19 @@ __device__ __forceinline__ void epilogue_tile(uint32_t acc, int quarter, int lan
                         __nv_bfloat162 h = __floats2bfloat162_rn((g0 / (1.0f + expf(-g0))) * u0, (g1 / (1.0f + expf(-g1))) * u1);
                         pk[j] = *reinterpret_cast<uint32_t*>(&h);
                     }
-                } else {
+                } else if (rope.gate_act == 1) {
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
                         const float g0 = v[4 * j], u0 = v[4 * j + 1], g1 = v[4 * j + 2], u1 = v[4 * j + 3];
                         __nv_bfloat162 h = __floats2bfloat162_rn(gated_pair(g0, u0, 1), gated_pair(g1, u1, 1));
+                        pk[j] = *reinterpret_cast<uint32_t*>(&h);
+                    }
+                } else {
+                    const float lim = rope.gate_limit, sl = rope.gate_slope;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        __nv_bfloat162 h = __floats2bfloat162_rn(gated_clamped(v[4 * j], v[4 * j + 1], lim, sl),
+                                                                 gated_clamped(v[4 * j + 2], v[4 * j + 3], lim, sl));
                         pk[j] = *reinterpret_cast<uint32_t*>(&h);
                     }
                 }
@@ -244,7 +259,9 @@ __device__ __forceinline__ void epilogue_tile(uint32_t acc, int quarter, int lan
             } else {
 #pragma unroll
                 for (int j = 0; j < 16; ++j)
-                    if (col + 2 * j + 1 < N) dst[j] = from_f32<TC>(gated_pair(v[2 * j], v[2 * j + 1], rope.gate_act));
+                    if (col + 2 * j + 1 < N)
+                        dst[j] = from_f32<TC>(rope.gate_act == 2 ? gated_clamped(v[2 * j], v[2 * j + 1], rope.gate_limit, rope.gate_slope)
+                                                                 : gated_pair(v[2 * j], v[2 * j + 1], rope.gate_act));
             }
         } else {
             TC* dst = C + (size_t)row * ldc + col;
@@ -817,10 +834,12 @@ static int launch_tc(const void* A, int lda, const void* W, int ldw, void* C, in
 
 template <int BN, int STAGES>
 static int launch_width(const void* A, int lda, const void* W, int ldw, void* C, int c_dtype, int ldc, int M, int N, int K,
-                        int epilogue, cudaStream_t stream, int gate_act = 0) {
+                        int epilogue, cudaStream_t stream, int gate_act = 0, float gate_limit = 0.f, float gate_slope = 0.f) {
     if (epilogue == 2) {
         RopeEpilogue gated = {};
         gated.gate_act = gate_act;
+        gated.gate_limit = gate_limit;
+        gated.gate_slope = gate_slope;
         return launch_tc<BN, STAGES, 2, __nv_bfloat16>(A, lda, W, ldw, C, ldc, M, N, K, stream, gated);
     }
     if (epilogue == 1) return launch_tc<BN, STAGES, 1, float>(A, lda, W, ldw, C, ldc, M, N, K, stream);
@@ -868,10 +887,12 @@ static int launch_pair(const void* A, int lda, const void* W, int ldw, void* C, 
 
 template <int BN, int STAGES>
 static int launch_pair_width(const void* A, int lda, const void* W, int ldw, void* C, int c_dtype, int ldc, int M, int N, int K,
-                             int epilogue, cudaStream_t stream, int gate_act = 0) {
+                             int epilogue, cudaStream_t stream, int gate_act = 0, float gate_limit = 0.f, float gate_slope = 0.f) {
     if (epilogue == 2) {
         RopeEpilogue gated = {};
         gated.gate_act = gate_act;
+        gated.gate_limit = gate_limit;
+        gated.gate_slope = gate_slope;
         return launch_pair<BN, STAGES, 2, __nv_bfloat16>(A, lda, W, ldw, C, ldc, M, N, K, stream, gated);
     }
     if (epilogue == 1) return launch_pair<BN, STAGES, 1, float>(A, lda, W, ldw, C, ldc, M, N, K, stream);
@@ -929,7 +950,7 @@ extern "C" int b200_gemm_tcgen05_status() {
 }
 
 // A, W bfloat16; C bfloat16 or float32; epilogue 0 store, 1 residual add (C float32), 2 gated SiLU (C bfloat16),
-// 3 gated GELU in its tanh form (C bfloat16).
+// 3 gated GELU in its tanh form (C bfloat16), 4 gated and clamped with gate_limit and gate_slope (C bfloat16).
 // Spans of K that the product's shape asks for (1: none).
 extern "C" int b200_gemm_tcgen05_k_spans(int M, int N, int K) {
     if (M <= 0 || N <= 0 || K <= 0) return 1;
@@ -941,13 +962,14 @@ extern "C" int b200_gemm_tcgen05_k_spans(int M, int N, int K) {
 // 0 lets the shape decide.
 // cta_pair: 1 computes 256-row tiles by pairs of CTAs (tile_width 256 or 128), -1 never does, 0 lets the shape decide.
 extern "C" int b200_gemm_tcgen05(const void* A, int lda, const void* W, int ldw, void* C, int c_dtype, int ldc, int M,
-                                 int N, int K, int epilogue, int tile_width, int k_spans, int cta_pair, cudaStream_t stream) {
+                                 int N, int K, int epilogue, int tile_width, int k_spans, int cta_pair, float gate_limit,
+                                 float gate_slope, cudaStream_t stream) {
     using namespace b200;
     if (M <= 0 || N <= 0) return 0;
     if (K < 8 || K % 8 != 0 || lda % 8 != 0 || ldw % 8 != 0 || (((uintptr_t)A | (uintptr_t)W) & 15)) return kErrUnsupportedSize;
     int gate_act = 0;
-    if (epilogue == 3) {   // the gated epilogue with GELU (tanh form) in place of SiLU; not in the kernel that cuts K into spans
-        gate_act = 1;
+    if (epilogue == 3 || epilogue == 4) {   // the gated epilogue with GELU (tanh form) or the clamped form in place of SiLU; not in the kernel that cuts K into spans
+        gate_act = epilogue - 2;
         epilogue = 2;
         if (k_spans > 1) return kErrBadArgument;
         k_spans = 1;
@@ -957,8 +979,8 @@ extern "C" int b200_gemm_tcgen05(const void* A, int lda, const void* W, int ldw,
     if (c_dtype != kF32 && c_dtype != kBF16) return kErrBadArgument;
     if (k_spans != 0 && k_spans != 1 && k_spans != 2 && k_spans != 4) return kErrBadArgument;
     if (cta_pair > 0) {
-        if (tile_width == 128) return launch_pair_width<128, 8>(A, lda, W, ldw, C, c_dtype, ldc, M, N, K, epilogue, stream, gate_act);
-        if (tile_width == 256 || tile_width == 0) return launch_pair_width<256, 6>(A, lda, W, ldw, C, c_dtype, ldc, M, N, K, epilogue, stream, gate_act);
+        if (tile_width == 128) return launch_pair_width<128, 8>(A, lda, W, ldw, C, c_dtype, ldc, M, N, K, epilogue, stream, gate_act, gate_limit, gate_slope);
+        if (tile_width == 256 || tile_width == 0) return launch_pair_width<256, 6>(A, lda, W, ldw, C, c_dtype, ldc, M, N, K, epilogue, stream, gate_act, gate_limit, gate_slope);
         return kErrBadArgument;
     }
     // left the choice: pairs of CTAs as soon as their 256 x 256 tiles occupy two thirds of the SMs (measured: from there on
@@ -966,7 +988,7 @@ extern "C" int b200_gemm_tcgen05(const void* A, int lda, const void* W, int ldw,
     if (cta_pair == 0 && tile_width == 0 && (k_spans == 0 || gate_act != 0)) {
         const long long pair_tiles = (long long)((M + 2 * BM - 1) / (2 * BM)) * ((N + 255) / 256);
         if (pair_tiles * 3 >= (long long)(sm_count() / 2) * 2) {
-            const int st = launch_pair_width<256, 6>(A, lda, W, ldw, C, c_dtype, ldc, M, N, K, epilogue, stream, gate_act);
+            const int st = launch_pair_width<256, 6>(A, lda, W, ldw, C, c_dtype, ldc, M, N, K, epilogue, stream, gate_act, gate_limit, gate_slope);
             if (st != kErrUnsupportedSize) return st;   // (no two SMs that can form a pair: the single-CTA kernels below)
         }
     }
@@ -980,9 +1002,9 @@ extern "C" int b200_gemm_tcgen05(const void* A, int lda, const void* W, int ldw,
     }
     // a stage holds 16 KB of A and BN / 8 KB of W: the narrower the tile, the deeper the ring
     const int width = tile_width > 0 ? tile_width : tile_width_for(M, N);
-    if (width == 256) return launch_width<256, 4>(A, lda, W, ldw, C, c_dtype, ldc, M, N, K, epilogue, stream, gate_act);
-    if (width == 128) return launch_width<128, 6>(A, lda, W, ldw, C, c_dtype, ldc, M, N, K, epilogue, stream, gate_act);
-    if (width == 64) return launch_width<64, 8>(A, lda, W, ldw, C, c_dtype, ldc, M, N, K, epilogue, stream, gate_act);
+    if (width == 256) return launch_width<256, 4>(A, lda, W, ldw, C, c_dtype, ldc, M, N, K, epilogue, stream, gate_act, gate_limit, gate_slope);
+    if (width == 128) return launch_width<128, 6>(A, lda, W, ldw, C, c_dtype, ldc, M, N, K, epilogue, stream, gate_act, gate_limit, gate_slope);
+    if (width == 64) return launch_width<64, 8>(A, lda, W, ldw, C, c_dtype, ldc, M, N, K, epilogue, stream, gate_act, gate_limit, gate_slope);
     return kErrBadArgument;
 }
 

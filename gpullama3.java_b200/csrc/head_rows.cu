@@ -1,9 +1,13 @@
 // What happens to the rows of a projection between the product and the attention kernels, for mixers whose
 // queries, keys, values or latents are not used as the product leaves them:
 //     z = x[src + r d .. + d] (+ bias)              one row of d numbers per (token, head)
-//     z <- z / sqrt(mean(z^2) + eps)                (optional: an RMS norm per row, 32-bit)
-//     z <- z * weight[0 .. d)                       (optional: the norm's weight, shared by the rows)
+//     z <- z / sqrt(mean(z^2) + eps)                (optional: an RMS norm per row, or one over all rows of the
+//                                                   segment at once, before they are split into heads; 32-bit)
+//     z <- z * weight[0 .. d)                       (optional: the norm's weight, shared by the rows or one per element
+//                                                   of the segment)
 //     z <- z * mul                                  (a score scale folded into the queries, or 1)
+//     z <- (1 - lambda) z + lambda other[...]       (optional: mixed with the same element of another layer's rows of the
+//                                                   same token, lambda a number in device memory; 32-bit)
 //     dst[dst_off + r d_pad .. + d_pad] = z, 0, ..., 0   (rows may be widened with zeros to the size a kernel takes)
 // A segment's rows go to a dense buffer (queries), or straight into the paged cache at the token's position: as key
 // rows ([page][kv_head][position][d_pad]) or as value rows (transposed, [page][kv_head][d_pad][position]), so that
@@ -20,10 +24,17 @@ constexpr int kRowThreads = 128;
 struct RowSegment {
     int src_off, n_rows, d, dst_off, d_pad;
     int bias_off;     // into `bias`, -1: none
-    int norm;         // 1: divide by the row's root mean square
+    int norm;         // 1: divide by the row's root mean square; 2: by that of all the segment's rows together
     int weight_off;   // into `weight`, -1: none
     float mul;
     int target;       // 0: dst; 1: key rows of the cache; 2: value rows of the cache
+    int weight_per_row;  // 1: the weight has n_rows * d entries (one per element of the segment), 0: d (shared by the rows)
+    int mix_off;      // column of `other` where this segment's counterpart starts, -1: no mixing
+};
+struct MixSource {
+    const void* other;      // [T][ld_other], the run's storage type
+    int ld_other;
+    const float* lambda;    // one number
 };
 struct CacheTarget {
     const int* positions;
@@ -42,7 +53,7 @@ struct RowSegments {
 template <typename T>
 __global__ void __launch_bounds__(kRowThreads)
 head_rows_kernel(const T* __restrict__ src, int ld_src, T* __restrict__ dst, int ld_dst, const float* __restrict__ bias,
-                 const float* __restrict__ weight, RowSegments segs, float eps, CacheTarget cache) {
+                 const float* __restrict__ weight, RowSegments segs, float eps, CacheTarget cache, MixSource mix) {
     const int t = blockIdx.x, lane = threadIdx.x & 31;
     int row = blockIdx.y * (kRowThreads / 32) + (threadIdx.x >> 5);
     if (row >= segs.total_rows) return;
@@ -55,7 +66,18 @@ head_rows_kernel(const T* __restrict__ src, int ld_src, T* __restrict__ dst, int
     const T* x = src + (size_t)t * ld_src + g.src_off + (size_t)row * g.d;
     const float* b = g.bias_off >= 0 ? bias + g.bias_off + (size_t)row * g.d : nullptr;
     float factor = g.mul;
-    if (g.norm) {
+    if (g.norm == 2) {   // every warp of the segment sums the whole segment, in the same order
+        const T* xs = src + (size_t)t * ld_src + g.src_off;
+        const float* bs = g.bias_off >= 0 ? bias + g.bias_off : nullptr;
+        const int n = g.n_rows * g.d;
+        float ss = 0.f;
+        for (int e = lane; e < n; e += 32) {
+            const float z = to_f32<T>(xs[e]) + (bs ? bs[e] : 0.f);
+            ss += z * z;
+        }
+        ss = warp_sum(ss);
+        factor *= 1.0f / sqrtf(ss / (float)n + eps);
+    } else if (g.norm) {
         float ss = 0.f;
         for (int e = lane; e < g.d; e += 32) {
             const float z = to_f32<T>(x[e]) + (b ? b[e] : 0.f);
@@ -64,7 +86,9 @@ head_rows_kernel(const T* __restrict__ src, int ld_src, T* __restrict__ dst, int
         ss = warp_sum(ss);
         factor *= 1.0f / sqrtf(ss / (float)g.d + eps);
     }
-    const float* w = g.weight_off >= 0 ? weight + g.weight_off : nullptr;
+    const float* w = g.weight_off >= 0 ? weight + g.weight_off + (g.weight_per_row ? (size_t)row * g.d : 0) : nullptr;
+    const T* other = g.mix_off >= 0 ? (const T*)mix.other + (size_t)t * mix.ld_other + g.mix_off + (size_t)row * g.d : nullptr;
+    const float lambda = other ? mix.lambda[0] : 0.f;
     T* o = dst + (size_t)t * ld_dst + g.dst_off + (size_t)row * g.d_pad;
     size_t step = 1;
     if (g.target != 0) {   // the row's place in the page of this token's position (n_rows = the cache's kv heads)
@@ -83,6 +107,7 @@ head_rows_kernel(const T* __restrict__ src, int ld_src, T* __restrict__ dst, int
         if (e < g.d) {
             z = (to_f32<T>(x[e]) + (b ? b[e] : 0.f)) * factor;
             if (w) z *= w[e];
+            if (other) z = (1.0f - lambda) * z + lambda * to_f32<T>(other[e]);
         }
         o[(size_t)e * step] = from_f32<T>(z);
     }
@@ -90,19 +115,20 @@ head_rows_kernel(const T* __restrict__ src, int ld_src, T* __restrict__ dst, int
 
 }  // namespace b200
 
-// `segments`: n_segments records of ten 32-bit words each (src_off, n_rows, d, dst_off, d_pad, bias_off, norm,
-// weight_off, mul as float bits, target), read on the host.  Segments with a cache target need positions, seq_ids,
+// `segments`: n_segments records of twelve 32-bit words each (src_off, n_rows, d, dst_off, d_pad, bias_off, norm,
+// weight_off, mul as float bits, target, weight_per_row, mix_off), read on the host.  Segments with a cache target need positions, seq_ids,
 // page_table and the pools; their n_rows is the number of kv heads of the cache entry and d_pad its head size.
 extern "C" int b200_head_rows(const void* src, int ld_src, void* dst, int ld_dst, int dtype, const float* bias,
                               const float* weight, const int* segments, int n_segments, int n_tokens, float eps,
                               const int* positions, const int* seq_ids, const int* page_table, int table_stride,
-                              void* k_pool, void* v_pool, cudaStream_t stream) {
+                              void* k_pool, void* v_pool, const void* other, int ld_other, const float* lambda,
+                              cudaStream_t stream) {
     if (n_tokens <= 0 || n_segments <= 0) return 0;
     if (n_segments > b200::kRowSegments) return b200::kErrBadArgument;
     b200::RowSegments segs = {};
     segs.n = n_segments;
     for (int i = 0; i < n_segments; ++i) {
-        const int* p = segments + 10 * i;
+        const int* p = segments + 12 * i;
         b200::RowSegment& g = segs.seg[i];
         g.src_off = p[0]; g.n_rows = p[1]; g.d = p[2]; g.dst_off = p[3]; g.d_pad = p[4];
         g.bias_off = p[5]; g.norm = p[6]; g.weight_off = p[7];
@@ -110,6 +136,10 @@ extern "C" int b200_head_rows(const void* src, int ld_src, void* dst, int ld_dst
         u.i = p[8];
         g.mul = u.f;
         g.target = p[9];
+        g.weight_per_row = p[10];
+        g.mix_off = p[11];
+        if (g.norm < 0 || g.norm > 2) return b200::kErrBadArgument;
+        if (g.mix_off >= 0 && (other == nullptr || lambda == nullptr)) return b200::kErrBadArgument;
         if (g.target < 0 || g.target > 2) return b200::kErrBadArgument;
         if (g.target != 0 && (!positions || !seq_ids || !page_table || (g.target == 1 ? !k_pool : !v_pool))) return b200::kErrBadArgument;
         if (g.target == 0 && dst == nullptr) return b200::kErrBadArgument;
@@ -122,8 +152,9 @@ extern "C" int b200_head_rows(const void* src, int ld_src, void* dst, int ld_dst
     dim3 grid(n_tokens, (segs.total_rows + per_cta - 1) / per_cta);
     if (grid.y > 65535) return b200::kErrUnsupportedSize;
     const b200::CacheTarget cache = {positions, seq_ids, page_table, table_stride, k_pool, v_pool};
+    const b200::MixSource mix = {other, ld_other, lambda};
     B200_DISPATCH_DTYPE(dtype, T,
         b200::head_rows_kernel<T><<<grid, b200::kRowThreads, 0, stream>>>((const T*)src, ld_src, (T*)dst, ld_dst, bias,
-                                                                          weight, segs, eps, cache));
+                                                                          weight, segs, eps, cache, mix));
     return b200::launch_status();
 }

@@ -1,4 +1,4 @@
-// RMSNorm over rows of the 32-bit residual stream.
+// RMSNorm, and further down layer norm, over rows of the 32-bit residual stream.
 //   ss = sum(x^2) / dim + eps ;  out = w * ((1 / sqrt(ss)) * x)
 // as inference/InferenceCore.java:47-56 of the reference project computes it (eps inside the root,
 // added after the mean; the weight multiplies plainly).  The sum of squares and the scale are
@@ -133,6 +133,131 @@ static int launch_norm_warp(const float* x, const void* w, void* out, const int*
                       stream, x, (const TW*)w, (TO*)out, rows, n_rows, eps);
 }
 
+// Layer norm with weight and bias over rows of the 32-bit residual stream:
+//   mu = mean(x) ;  var = mean((x - mu)^2) ;  out = (x - mu) / sqrt(var + eps) * w + b
+// The variance is the mean of the squared deviations from the mean (two sums over values held in registers, not
+// E[x^2] - mu^2); both sums and the result are 32-bit, weight and bias are 32-bit numbers.
+template <typename TO, bool VEC>
+__global__ void __launch_bounds__(kNormThreads)
+layernorm_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b, TO* __restrict__ out,
+                 const int* __restrict__ rows, int dim, float eps) {
+    __shared__ float scratch[33];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int r = blockIdx.x;
+    const float* xr = x + (size_t)(rows ? rows[r] : r) * dim;
+    TO* o = out + (size_t)r * dim;
+    if (VEC) {
+        float keep[kNormKeep][4];
+        float s = 0.f;
+#pragma unroll
+        for (int k = 0; k < kNormKeep; ++k) {
+            const int i = (k * kNormThreads + threadIdx.x) * 4;
+            if (i < dim) {
+                load4<float>(xr + i, keep[k]);
+                s += (keep[k][0] + keep[k][1]) + (keep[k][2] + keep[k][3]);
+            }
+        }
+        for (int i = (kNormKeep * kNormThreads + threadIdx.x) * 4; i < dim; i += kNormThreads * 4) {
+            float v[4];
+            load4<float>(xr + i, v);
+            s += (v[0] + v[1]) + (v[2] + v[3]);
+        }
+        const float mu = block_sum(s, scratch) / (float)dim;
+        float ss = 0.f;
+#pragma unroll
+        for (int k = 0; k < kNormKeep; ++k) {
+            const int i = (k * kNormThreads + threadIdx.x) * 4;
+            if (i < dim) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) { keep[k][e] -= mu; ss += keep[k][e] * keep[k][e]; }
+            }
+        }
+        for (int i = (kNormKeep * kNormThreads + threadIdx.x) * 4; i < dim; i += kNormThreads * 4) {
+            float v[4];
+            load4<float>(xr + i, v);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) ss += (v[e] - mu) * (v[e] - mu);
+        }
+        const float scale = 1.0f / sqrtf(block_sum(ss, scratch) / (float)dim + eps);
+#pragma unroll
+        for (int k = 0; k < kNormKeep; ++k) {
+            const int i = (k * kNormThreads + threadIdx.x) * 4;
+            if (i < dim) {
+                float wv[4], bv[4], y[4];
+                load4<float>(w + i, wv);
+                load4<float>(b + i, bv);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) y[e] = keep[k][e] * scale * wv[e] + bv[e];
+                store4<TO>(o + i, y);
+            }
+        }
+        for (int i = (kNormKeep * kNormThreads + threadIdx.x) * 4; i < dim; i += kNormThreads * 4) {
+            float v[4], wv[4], bv[4], y[4];
+            load4<float>(xr + i, v);
+            load4<float>(w + i, wv);
+            load4<float>(b + i, bv);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) y[e] = (v[e] - mu) * scale * wv[e] + bv[e];
+            store4<TO>(o + i, y);
+        }
+    } else {
+        float s = 0.f, ss = 0.f;
+        for (int i = threadIdx.x; i < dim; i += blockDim.x) s += xr[i];
+        const float mu = block_sum(s, scratch) / (float)dim;
+        for (int i = threadIdx.x; i < dim; i += blockDim.x) { const float d = xr[i] - mu; ss += d * d; }
+        const float scale = 1.0f / sqrtf(block_sum(ss, scratch) / (float)dim + eps);
+        for (int i = threadIdx.x; i < dim; i += blockDim.x) o[i] = from_f32<TO>((xr[i] - mu) * scale * w[i] + b[i]);
+    }
+}
+
+// The same with a warp per row (dim = 128 * KEEP), as rmsnorm_warp_kernel.
+template <typename TO, int KEEP>
+__global__ void __launch_bounds__(kNormWarps * 32)
+layernorm_warp_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b,
+                      TO* __restrict__ out, const int* __restrict__ rows, int n_rows, float eps) {
+    constexpr int dim = KEEP * 128;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int r = blockIdx.x * kNormWarps + (threadIdx.x >> 5);
+    if (r >= n_rows) return;
+    const float* xr = x + (size_t)(rows ? rows[r] : r) * dim;
+    float keep[KEEP][4];
+    float s = 0.f, ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < KEEP; ++k) load4<float>(xr + (k * 32 + lane) * 4, keep[k]);
+#pragma unroll
+    for (int k = 0; k < KEEP; ++k) s += (keep[k][0] + keep[k][1]) + (keep[k][2] + keep[k][3]);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+    const float mu = s / (float)dim;
+#pragma unroll
+    for (int k = 0; k < KEEP; ++k)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { keep[k][e] -= mu; ss += keep[k][e] * keep[k][e]; }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+    const float scale = 1.0f / sqrtf(ss / (float)dim + eps);
+    TO* o = out + (size_t)r * dim;
+#pragma unroll
+    for (int k = 0; k < KEEP; ++k) {
+        float wv[4], bv[4], y[4];
+        load4<float>(w + (k * 32 + lane) * 4, wv);
+        load4<float>(b + (k * 32 + lane) * 4, bv);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) y[e] = keep[k][e] * scale * wv[e] + bv[e];
+        store4<TO>(o + (k * 32 + lane) * 4, y);
+    }
+}
+
+template <typename TO, int KEEP>
+static int launch_layernorm_warp(const float* x, const float* w, const float* b, void* out, const int* rows, int n_rows,
+                                 float eps, cudaStream_t stream) {
+    return launch_pdl(layernorm_warp_kernel<TO, KEEP>, dim3((n_rows + kNormWarps - 1) / kNormWarps), dim3(kNormWarps * 32), 0,
+                      stream, x, w, b, (TO*)out, rows, n_rows, eps);
+}
+
 }  // namespace b200
 
 extern "C" int b200_rmsnorm(const float* x, const void* w, int w_dtype, void* out, int out_dtype,
@@ -153,5 +278,28 @@ extern "C" int b200_rmsnorm(const float* x, const void* w, int w_dtype, void* ou
                                       (const TW*)w, (TO*)out, rows, dim, eps)
                    : b200::launch_pdl(b200::rmsnorm_kernel<TW, TO, false>, dim3(n_rows), dim3(b200::kNormThreads), 0, stream, x,
                                       (const TW*)w, (TO*)out, rows, dim, eps)));
+    return b200::launch_status();
+}
+
+// Layer norm of rows of the 32-bit residual stream; weight and bias are 32-bit.
+extern "C" int b200_layernorm(const float* x, const float* w, const float* b, void* out, int out_dtype, const int* rows,
+                              int n_rows, int dim, float eps, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (dim < 1 || !w || !b) return b200::kErrBadArgument;
+    const bool vec = dim % 4 == 0 && ((((uintptr_t)x) | ((uintptr_t)w) | ((uintptr_t)b) | ((uintptr_t)out)) & 15) == 0;
+    if (vec && n_rows >= 1024 && dim % 1024 == 0 && dim <= 4096) {
+        B200_DISPATCH_DTYPE(out_dtype, TO,
+            switch (dim / 1024) {
+                case 1: return b200::launch_layernorm_warp<TO, 8>(x, w, b, out, rows, n_rows, eps, stream);
+                case 2: return b200::launch_layernorm_warp<TO, 16>(x, w, b, out, rows, n_rows, eps, stream);
+                case 3: return b200::launch_layernorm_warp<TO, 24>(x, w, b, out, rows, n_rows, eps, stream);
+                default: return b200::launch_layernorm_warp<TO, 32>(x, w, b, out, rows, n_rows, eps, stream);
+            });
+    }
+    B200_DISPATCH_DTYPE(out_dtype, TO,
+        return vec ? b200::launch_pdl(b200::layernorm_kernel<TO, true>, dim3(n_rows), dim3(b200::kNormThreads), 0, stream, x, w, b,
+                                      (TO*)out, rows, dim, eps)
+                   : b200::launch_pdl(b200::layernorm_kernel<TO, false>, dim3(n_rows), dim3(b200::kNormThreads), 0, stream, x, w, b,
+                                      (TO*)out, rows, dim, eps));
     return b200::launch_status();
 }

@@ -25,7 +25,7 @@ class CausalLM:
         if dtype not in (torch.float32, torch.bfloat16):
             raise ConfigError(f"the engine runs in float32 or bfloat16, not {dtype}")
         self.config, self.dtype, self.device = config, dtype, torch.device(device)
-        self.embedding = TokenEmbedding(config.vocab_size, config.hidden_size)
+        self.embedding = TokenEmbedding(config.vocab_size, config.hidden_size, scale=config.embedding_scale())
         self.blocks: list[Block] = [build_block(s) for s in config.layer_specs()]
         self.final_norm = build_part(config.final_norm())
         self.head = OutputHead(config.vocab_size, config.hidden_size,

@@ -11,18 +11,18 @@ import torch
 from . import ops
 
 
-def try_gemm(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int) -> bool:
+def try_gemm(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int, gate_args=(0.0, 0.0)) -> bool:
     if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         return False
     M = a.shape[0]
     if M <= 16:
-        return ops.gemm_decode(a, w, c, epilogue)
-    # (the few-token tensor-core kernel has the gated epilogue with SiLU only; with GELU those sizes go to the other two)
-    if M <= 128 and epilogue != ops.EPILOGUE_GATED_GELU_TANH and ops.gemm_skinny(a, w, c, epilogue):
+        return ops.gemm_decode(a, w, c, epilogue, gate_args)
+    # (the few-token tensor-core kernel has the gated epilogue with SiLU only; the other activations' sizes go to the other two)
+    if M <= 128 and epilogue in (ops.EPILOGUE_STORE, ops.EPILOGUE_RESIDUAL_ADD, ops.EPILOGUE_GATED_SILU) and ops.gemm_skinny(a, w, c, epilogue):
         return True
-    if M <= 64 and ops.gemm_decode(a, w, c, epilogue):
+    if M <= 64 and ops.gemm_decode(a, w, c, epilogue, gate_args):
         return True
-    return ops.gemm_tcgen05(a, w, c, epilogue)
+    return ops.gemm_tcgen05(a, w, c, epilogue, gate_args=gate_args)
 
 
 def try_projection_with_rope(x: torch.Tensor, w: torch.Tensor, qkv: torch.Tensor, ctx, page_table, cache, mixer,
@@ -53,7 +53,9 @@ def try_decode_attention_with_rope(qkv, out, ctx, page_table, cache, mixer, writ
     return True
 
 
-def try_attention(qkv, out, ctx, page_table, cache, mixer) -> bool:
+def try_attention(qkv, out, ctx, page_table, cache, mixer, gate=None) -> bool:
+    if getattr(mixer, "has_terms", False):   # kept first positions, distance penalty, sink, output gate: the plain kernel
+        return False
     if ctx.all_decode and ops.attention_decode_supported(qkv.dtype, mixer.n_heads, mixer.n_kv_heads, mixer.head_dim):
         splits, early = mixer.plan_decode(ctx, cache)
         ops.attention_decode(qkv, qkv.shape[1], out, ctx.kv_lens, page_table, cache.k, cache.v, mixer.n_heads,

@@ -34,25 +34,25 @@ _functions: dict[str, ctypes._CFuncPtr] = {}
 
 # C signatures: library, then argument types (the trailing stream is added for all)
 _SIGNATURES = {
-    "b200_embed_gather": ("embedding", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int]),
+    "b200_embed_gather": ("embedding", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float]),
     "b200_rmsnorm": ("norm", [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_float]),
     "b200_rope_cache_write": ("rope_cache", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                              c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int]),
     "b200_attention_paged": ("attention_generic", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                                    c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-                                                   c_void_p]),
+                                                   c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int]),
     "b200_gemm_generic": ("gemm_generic", [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int,
-                                           c_int, c_int, c_int, c_int]),
+                                           c_int, c_int, c_int, c_int, c_float, c_float]),
     "b200_gemm_generic_batched": ("gemm_generic", [c_void_p, c_int, c_int, ctypes.c_longlong, c_void_p, c_int, c_int,
                                                    ctypes.c_longlong, c_void_p, c_int, c_int, ctypes.c_longlong, c_int, c_int,
                                                    c_int, c_int]),
     "b200_gemm_decode": ("gemm_decode", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                                         c_int]),
+                                         c_int, c_float, c_float]),
     "b200_gemm_decode_linked": ("gemm_decode", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
                                                 c_int, c_int, c_void_p, c_int, c_float, c_int, c_void_p, c_int, c_void_p,
                                                 c_int, c_void_p]),
     "b200_gemm_tcgen05": ("gemm_tcgen05", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                                           c_int, c_int, c_int, c_int]),
+                                           c_int, c_int, c_int, c_int, c_float, c_float]),
     "b200_gemm_tcgen05_qkv_rope": ("gemm_tcgen05", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p,
                                                     c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                                     c_int, c_int, c_int]),
@@ -77,15 +77,24 @@ _SIGNATURES = {
     "b200_streams_step": ("streams", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                       c_int, c_int, c_float]),
     "b200_head_rows": ("head_rows", [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
-                                     c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
+                                     c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                                     c_void_p]),
     "b200_softcap_rows": ("elementwise", [c_void_p, ctypes.c_longlong, c_float]),
     "b200_gated_rmsnorm": ("elementwise", [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
-                                           c_float]),
+                                           c_float, c_int]),
+    "b200_layernorm": ("norm", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float]),
     "b200_causal_conv_silu": ("delta_rule", [c_void_p, c_int, c_void_p, c_void_p, ctypes.c_longlong, c_void_p, c_void_p,
                                              c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int]),
     "b200_delta_rule_scan": ("delta_rule", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                             ctypes.c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-                                            c_int, c_int, c_int, c_int, c_float, c_float]),
+                                            c_int, c_int, c_int, c_int, c_float, c_float, c_int]),
+    "b200_moe_route": ("moe", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                               c_int, c_int, c_float]),
+    "b200_moe_experts": ("moe", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                 c_int, c_int, c_int, c_int, c_float, c_float]),
+    "b200_moe_group": ("moe", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "b200_moe_gather": ("moe", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int]),
+    "b200_moe_combine": ("moe", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int]),
     "b200_argmax_rows": ("sampling", [c_void_p, c_int, c_void_p, c_int, c_int]),
     "b200_sample_rows": ("sampling", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_void_p]),
 }
@@ -195,14 +204,14 @@ def _dev(*tensors: torch.Tensor) -> None:
 
 
 # --------------------------------------------------------------------------- embedding, norm
-def embed_gather(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor) -> None:
-    """out[t] = table[tokens[t]] into the float32 residual stream.  tokens int32 [T]."""
+def embed_gather(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, scale: float = 1.0) -> None:
+    """out[t] = scale * table[tokens[t]] into the float32 residual stream.  tokens int32 [T]."""
     _dev(table, tokens, out)
     assert out.dtype == torch.float32 and tokens.dtype == torch.int32
     assert table.is_contiguous() and out.is_contiguous()
     n, dim = out.shape
     _check(_fn("b200_embed_gather")(table.data_ptr(), dtype_code(table.dtype), tokens.data_ptr(), out.data_ptr(),
-                                    n, dim, table.shape[0], _stream()), "embed_gather")
+                                    n, dim, table.shape[0], float(scale), _stream()), "embed_gather")
 
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float, rows: torch.Tensor | None = None) -> None:
@@ -216,6 +225,21 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float
     _check(_fn("b200_rmsnorm")(x.data_ptr(), weight.data_ptr(), dtype_code(weight.dtype), out.data_ptr(),
                                dtype_code(out.dtype), rows.data_ptr() if rows is not None else None, n_rows, dim,
                                float(eps), _stream()), "rmsnorm")
+
+
+def layernorm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, out: torch.Tensor, eps: float,
+              rows: torch.Tensor | None = None) -> None:
+    """out[r] = (x[rows[r]] - mean) / sqrt(mean((x - mean)^2) + eps) * weight + bias.  x, weight, bias float32."""
+    _dev(x, weight, bias, out, rows)
+    assert x.dtype == weight.dtype == bias.dtype == torch.float32
+    assert x.is_contiguous() and out.is_contiguous() and weight.is_contiguous() and bias.is_contiguous()
+    n_rows, dim = out.shape
+    assert x.shape[1] == dim and weight.numel() == dim and bias.numel() == dim
+    if rows is not None:
+        assert rows.dtype == torch.int32 and rows.numel() == n_rows
+    _check(_fn("b200_layernorm")(x.data_ptr(), weight.data_ptr(), bias.data_ptr(), out.data_ptr(), dtype_code(out.dtype),
+                                 rows.data_ptr() if rows is not None else None, n_rows, dim, float(eps), _stream()),
+           "layernorm")
 
 
 # --------------------------------------------------------------------------- position encoding + cache write
@@ -243,11 +267,15 @@ def rope_cache_write(qkv: torch.Tensor, positions: torch.Tensor, seq_ids: torch.
 # --------------------------------------------------------------------------- attention
 def attention_paged(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, positions: torch.Tensor,
                     seq_ids: torch.Tensor, page_table: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
-                    n_heads: int, n_kv_heads: int, head_dim: int, window: int = 0, n_splits: int = 1) -> None:
+                    n_heads: int, n_kv_heads: int, head_dim: int, window: int = 0, n_splits: int = 1, *,
+                    keep_first: int = 0, slopes: torch.Tensor | None = None, sinks: torch.Tensor | None = None,
+                    gate: torch.Tensor | None = None) -> None:
     """Causal grouped-query attention of every token of ``q`` over the cached keys 0..position of
     its sequence.  q: rows of ``q_row_stride`` elements whose first H*D are the rotated queries.
     ``n_splits`` > 1 cuts every token's keys into that many spans, one CTA each, merged by a second kernel (a decode
-    step: few tokens, long rows of keys)."""
+    step: few tokens, long rows of keys).  ``keep_first``: positions below it stay visible behind the window;
+    ``slopes`` float32 [H]: score -= slopes[h] * distance; ``sinks`` float32 [H]: exp(sinks[h]) joins the softmax's
+    denominator; ``gate`` [T, >= H] of q's dtype: head outputs are multiplied by sigmoid(gate[t, h])."""
     _dev(q, out, positions, seq_ids, page_table, k_pool, v_pool)
     assert out.is_contiguous() and out.shape[1] == n_heads * head_dim and out.dtype == q.dtype == k_pool.dtype
     assert tuple(k_pool.shape[1:]) == (n_kv_heads, PAGE_TOKENS, head_dim)
@@ -255,20 +283,30 @@ def attention_paged(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, posit
     scratch = None
     if n_splits > 1:
         scratch = torch.empty(out.shape[0] * n_heads * n_splits * (head_dim + 2), dtype=torch.float32, device=q.device)
+    _dev(slopes, sinks, gate)
+    for t in (slopes, sinks):
+        assert t is None or (t.dtype == torch.float32 and t.is_contiguous() and t.numel() == n_heads)
+    assert gate is None or (gate.dtype == q.dtype and gate.stride(1) == 1 and gate.shape[1] >= n_heads)
+    ptr = lambda t: t.data_ptr() if t is not None else None
     _check(_fn("b200_attention_paged")(
         q.data_ptr(), q_row_stride, out.data_ptr(), dtype_code(q.dtype), positions.data_ptr(), seq_ids.data_ptr(),
         page_table.data_ptr(), page_table.shape[1], k_pool.data_ptr(), v_pool.data_ptr(), out.shape[0], n_heads,
-        n_kv_heads, head_dim, int(window), int(n_splits), scratch.data_ptr() if scratch is not None else None, _stream()),
+        n_kv_heads, head_dim, int(window), int(n_splits), scratch.data_ptr() if scratch is not None else None,
+        int(keep_first), ptr(slopes), ptr(sinks), ptr(gate), gate.stride(0) if gate is not None else 0, _stream()),
         "attention_paged")
 
 
 # --------------------------------------------------------------------------- matrix products
-EPILOGUE_STORE, EPILOGUE_RESIDUAL_ADD, EPILOGUE_GATED_SILU, EPILOGUE_GATED_GELU_TANH = 0, 1, 2, 3
-GATED_EPILOGUES = (EPILOGUE_GATED_SILU, EPILOGUE_GATED_GELU_TANH)
-ACTIVATION_CODES = {"silu": 0, "gelu_tanh": 1}   # the gated epilogues' activations of the gate value
+EPILOGUE_STORE, EPILOGUE_RESIDUAL_ADD, EPILOGUE_GATED_SILU, EPILOGUE_GATED_GELU_TANH, EPILOGUE_GATED_CLAMPED = 0, 1, 2, 3, 4
+GATED_EPILOGUES = (EPILOGUE_GATED_SILU, EPILOGUE_GATED_GELU_TANH, EPILOGUE_GATED_CLAMPED)
+# the gated epilogues' activations: silu(g) u, gelu_tanh(g) u, and the clamped form g' sigmoid(slope g') (u' + 1) with
+# g' = min(g, limit), u' = clamp(u, -limit, limit), whose two numbers travel with the call (``gate_args``)
+ACTIVATION_CODES = {"silu": 0, "gelu_tanh": 1, "clamped_sigmoid": 2}
+GATED_EPILOGUE_OF = {"silu": EPILOGUE_GATED_SILU, "gelu_tanh": EPILOGUE_GATED_GELU_TANH, "clamped_sigmoid": EPILOGUE_GATED_CLAMPED}
 
 
-def gemm_generic(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int = EPILOGUE_STORE) -> None:
+def gemm_generic(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int = EPILOGUE_STORE,
+                 gate_args: tuple[float, float] = (0.0, 0.0)) -> None:
     """c = a @ w.T (store), c += a @ w.T (residual add, c float32) or c = act(gate) * up with
     gate/up rows interleaved in w (act: SiLU, or GELU in its tanh form).  32-bit FMA accumulation, no tensor cores."""
     _dev(a, w, c)
@@ -278,7 +316,8 @@ def gemm_generic(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: in
     assert c.shape[0] == M and c.shape[1] == (N // 2 if epilogue in GATED_EPILOGUES else N)
     _check(_fn("b200_gemm_generic")(
         a.data_ptr(), dtype_code(a.dtype), a.stride(0), w.data_ptr(), dtype_code(w.dtype), w.stride(0), c.data_ptr(),
-        dtype_code(c.dtype), c.stride(0), M, N, K, epilogue, _stream()), "gemm_generic")
+        dtype_code(c.dtype), c.stride(0), M, N, K, epilogue, float(gate_args[0]), float(gate_args[1]), _stream()),
+        "gemm_generic")
 
 
 def gemm_per_head(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor) -> None:
@@ -294,7 +333,8 @@ def gemm_per_head(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor) -> None:
                                             T, n, k, H, _stream()), "gemm_per_head")
 
 
-def gemm_decode(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int = EPILOGUE_STORE) -> bool:
+def gemm_decode(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int = EPILOGUE_STORE,
+                gate_args: tuple[float, float] = (0.0, 0.0)) -> bool:
     """The decode-step matrix product (bfloat16 operands, at most 64 tokens, K a multiple of 32).
     Returns False, having done nothing, for operands it does not take."""
     M, K = a.shape
@@ -306,7 +346,8 @@ def gemm_decode(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int
     assert w.shape[1] == K and c.stride(1) == 1 and c.shape[0] == M
     assert c.shape[1] == (N // 2 if epilogue in GATED_EPILOGUES else N)
     _check(_fn("b200_gemm_decode")(a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), c.data_ptr(),
-                                   dtype_code(c.dtype), c.stride(0), M, N, K, epilogue, _stream()), "gemm_decode")
+                                   dtype_code(c.dtype), c.stride(0), M, N, K, epilogue, float(gate_args[0]),
+                                   float(gate_args[1]), _stream()), "gemm_decode")
     return True
 
 
@@ -357,7 +398,8 @@ def gemm_decode_linked(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilog
 
 
 def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int = EPILOGUE_STORE,
-                 tile_width: int = 0, k_spans: int = 0, cta_pair: int = 0) -> bool:
+                 tile_width: int = 0, k_spans: int = 0, cta_pair: int = 0,
+                 gate_args: tuple[float, float] = (0.0, 0.0)) -> bool:
     """The prefill matrix product on tcgen05 tensor cores (bfloat16 operands, rows 16-byte aligned).
     ``tile_width``: 256, 128 or 64 output columns per tile; 0 lets the shape decide (narrower tiles when the
     widest would leave SMs without one).  ``k_spans``: 2 or 4 cuts K among the CTAs of a cluster, which add their
@@ -379,7 +421,8 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: in
     ldc, c_inner = c.stride()
     assert Kw == K and c_inner == 1 and c.shape == (M, N // 2 if epilogue in GATED_EPILOGUES else N)
     _check(_fn("b200_gemm_tcgen05")(pa, lda, pw, ldw, c.data_ptr(), dtype_code(c.dtype), ldc, M, N, K, epilogue,
-                                    tile_width, k_spans, cta_pair, _stream()), "gemm_tcgen05")
+                                    tile_width, k_spans, cta_pair, float(gate_args[0]), float(gate_args[1]), _stream()),
+           "gemm_tcgen05")
     return True
 
 
@@ -445,7 +488,7 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int
     if (a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or M > 128 or K % 8 or K < 8 or a.stride(1) != 1
             or w.stride(1) != 1 or a.stride(0) % 8 or w.stride(0) % 8 or (a.data_ptr() | w.data_ptr()) & 15):
         return False
-    if epilogue == EPILOGUE_GATED_GELU_TANH or (epilogue == EPILOGUE_GATED_SILU and c.dtype != torch.bfloat16):
+    if epilogue in (EPILOGUE_GATED_GELU_TANH, EPILOGUE_GATED_CLAMPED) or (epilogue == EPILOGUE_GATED_SILU and c.dtype != torch.bfloat16):
         return False
     _dev(a, w, c)
     N = w.shape[0]
@@ -715,22 +758,29 @@ def streams_step(x: torch.Tensor, mix: torch.Tensor, write: torch.Tensor, y: tor
 TO_ROWS, TO_CACHE_KEYS, TO_CACHE_VALUES = 0, 1, 2
 
 
+ROW_WORDS = 12   # 32-bit words of one segment record (head_rows.cu)
+
+
 def head_row_segment(src_off: int, n_rows: int, d: int, dst_off: int, d_pad: int | None = None, bias_off: int = -1,
-                     norm: bool = False, weight_off: int = -1, mul: float = 1.0, target: int = TO_ROWS) -> list[int]:
+                     norm: bool | int = False, weight_off: int = -1, mul: float = 1.0, target: int = TO_ROWS,
+                     weight_per_row: bool = False, mix_off: int = -1) -> list[int]:
     """One segment of ``head_rows``: ``n_rows`` rows of ``d`` numbers from column ``src_off`` on, each (+ bias)
     (normalised) (* weight) * mul, written ``d_pad`` wide (zeros behind the ``d``) from column ``dst_off`` on, or with
     ``target`` TO_CACHE_KEYS / TO_CACHE_VALUES into the cache page of the token's position (``n_rows`` = the cache
-    entry's kv heads, ``d_pad`` its head size)."""
+    entry's kv heads, ``d_pad`` its head size).  ``norm``: True / 1 per row, 2 over all rows of the segment at once
+    (the weight then usually has an entry per element: ``weight_per_row``).  ``mix_off``: the column of ``head_rows``'s
+    ``other`` rows this segment is mixed with."""
     import struct
 
-    return [src_off, n_rows, d, dst_off, d if d_pad is None else d_pad, bias_off, 1 if norm else 0, weight_off,
-            struct.unpack("<i", struct.pack("<f", float(mul)))[0], target]
+    return [src_off, n_rows, d, dst_off, d if d_pad is None else d_pad, bias_off, int(norm), weight_off,
+            struct.unpack("<i", struct.pack("<f", float(mul)))[0], target, 1 if weight_per_row else 0, mix_off]
 
 
 def head_rows(src: torch.Tensor, dst: torch.Tensor | None, segments, eps: float = 0.0, bias: torch.Tensor | None = None,
-              weight: torch.Tensor | None = None, cache=None) -> None:
+              weight: torch.Tensor | None = None, cache=None, mix=None) -> None:
     """``segments``: a ctypes array made by ``head_row_segments`` (at most four segments).  ``cache``: (positions,
-    seq_ids, page_table, k_pool, v_pool) for segments that go into the paged cache; ``dst`` may be None when all do."""
+    seq_ids, page_table, k_pool, v_pool) for segments that go into the paged cache; ``dst`` may be None when all do.
+    ``mix``: (other [T, >= ...] of src's dtype, lambda float32 [1]) for segments with a ``mix_off``."""
     _dev(src, dst, bias, weight)
     assert src.stride(1) == 1
     assert dst is None or (src.dtype == dst.dtype and dst.stride(1) == 1 and src.shape[0] == dst.shape[0])
@@ -742,11 +792,18 @@ def head_rows(src: torch.Tensor, dst: torch.Tensor | None, segments, eps: float 
         _dev(pos, seq, table, k_pool, v_pool)
         assert pos.dtype == seq.dtype == table.dtype == torch.int32 and table.dim() == 2 and table.is_contiguous()
         assert k_pool.dtype == v_pool.dtype == src.dtype and k_pool.is_contiguous() and v_pool.is_contiguous()
+    other = lam = None
+    if mix is not None:
+        other, lam = mix
+        _dev(other, lam)
+        assert other.dtype == src.dtype and other.stride(1) == 1 and other.shape[0] == src.shape[0]
+        assert lam.dtype == torch.float32 and lam.numel() == 1
     ptr = lambda t: t.data_ptr() if t is not None else None
     _check(_fn("b200_head_rows")(src.data_ptr(), src.stride(0), ptr(dst), dst.stride(0) if dst is not None else 0,
                                  dtype_code(src.dtype), ptr(bias), ptr(weight), ctypes.addressof(segments),
-                                 len(segments) // 10, src.shape[0], float(eps), ptr(pos), ptr(seq), ptr(table),
-                                 table.shape[1] if table is not None else 0, ptr(k_pool), ptr(v_pool), _stream()), "head_rows")
+                                 len(segments) // ROW_WORDS, src.shape[0], float(eps), ptr(pos), ptr(seq), ptr(table),
+                                 table.shape[1] if table is not None else 0, ptr(k_pool), ptr(v_pool), ptr(other),
+                                 other.stride(0) if other is not None else 0, ptr(lam), _stream()), "head_rows")
 
 
 def head_row_segments(*segments: list[int]):
@@ -763,15 +820,20 @@ def softcap_rows(logits: torch.Tensor, cap: float) -> None:
     _check(_fn("b200_softcap_rows")(logits.data_ptr(), logits.numel(), float(cap), _stream()), "softcap_rows")
 
 
+GATE_ACTIVATIONS = {"sigmoid": 0, "silu": 1}
+
+
 def gated_rmsnorm(x: torch.Tensor, weight: torch.Tensor, gate: torch.Tensor, out: torch.Tensor, n_heads: int, d: int,
-                  eps: float) -> None:
-    """Per (token, head) row of float32 x [T, n_heads d]: x / sqrt(mean(x^2) + eps) * weight[d] * sigmoid(gate)."""
+                  eps: float, activation: str = "sigmoid") -> None:
+    """Per (token, head) row of float32 x [T, n_heads d]: x / sqrt(mean(x^2) + eps) * weight[d] * act(gate), act the
+    sigmoid or SiLU."""
     _dev(x, weight, gate, out)
     assert x.dtype == weight.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous() and gate.stride(1) == 1
     assert x.shape[1] == n_heads * d == out.shape[1] and gate.shape[1] >= n_heads * d and weight.numel() == d
     assert gate.dtype == out.dtype
     _check(_fn("b200_gated_rmsnorm")(x.data_ptr(), weight.data_ptr(), gate.data_ptr(), gate.stride(0), out.data_ptr(),
-                                     dtype_code(out.dtype), x.shape[0], n_heads, d, float(eps), _stream()), "gated_rmsnorm")
+                                     dtype_code(out.dtype), x.shape[0], n_heads, d, float(eps),
+                                     GATE_ACTIVATIONS[activation], _stream()), "gated_rmsnorm")
 
 
 # --------------------------------------------------------------------------- short convolution and the delta rule
@@ -804,15 +866,17 @@ def delta_rule_supported(d_k: int) -> bool:
 def delta_rule_scan(qkv: torch.Tensor, beta: torch.Tensor, decay: torch.Tensor, dt_bias: torch.Tensor,
                     a_log: torch.Tensor, state: torch.Tensor, slots: torch.Tensor, cu_seqlens: torch.Tensor,
                     out: torch.Tensor, heads: int, kv_heads: int, d_k: int, d_v: int, q_scale: float,
-                    unit_eps: float, alloc=None) -> None:
+                    unit_eps: float, alloc=None, decay_per_head: bool = False) -> None:
     """The gated delta rule over a packed step.  qkv [T, 2 kv_heads d_k + heads d_v] (after the convolution), beta
     [T, >= heads] and decay [T, >= heads d_k] as the projections leave them, state float32 [slots, >= heads d_k d_v]
-    (updated in place), out float32 [T, heads d_v].  ``alloc(shape, dtype)``: where the scan's scratch (a row of
+    (updated in place), out float32 [T, heads d_v].  ``decay_per_head``: decay [T, >= heads] and dt_bias [heads], one
+    decay for all key channels of a head.  ``alloc(shape, dtype)``: where the scan's scratch (a row of
     32-bit numbers per token and head) comes from."""
     _dev(qkv, beta, decay, dt_bias, a_log, state, slots, cu_seqlens, out)
     assert qkv.dtype == beta.dtype == decay.dtype and qkv.stride(1) == beta.stride(1) == decay.stride(1) == 1
     assert dt_bias.dtype == a_log.dtype == state.dtype == out.dtype == torch.float32 and out.is_contiguous()
-    assert dt_bias.numel() == heads * d_k and a_log.numel() == heads and state.stride(1) == 1
+    assert dt_bias.numel() == (heads if decay_per_head else heads * d_k) and a_log.numel() == heads and state.stride(1) == 1
+    assert decay.shape[1] >= (heads if decay_per_head else heads * d_k)
     assert state.shape[1] >= heads * d_k * d_v and out.shape[1] == heads * d_v and out.shape[0] == qkv.shape[0]
     lib = library("delta_rule")
     shape = (heads, qkv.shape[0], int(lib.b200_delta_rule_row(c_int(d_k), c_int(d_v))))
@@ -821,4 +885,73 @@ def delta_rule_scan(qkv: torch.Tensor, beta: torch.Tensor, decay: torch.Tensor, 
                                        decay.stride(0), dt_bias.data_ptr(), a_log.data_ptr(), state.data_ptr(),
                                        state.stride(0), slots.data_ptr(), cu_seqlens.data_ptr(), out.data_ptr(),
                                        scratch.data_ptr(), dtype_code(qkv.dtype), qkv.shape[0], slots.numel(), heads,
-                                       kv_heads, d_k, d_v, float(q_scale), float(unit_eps), _stream()), "delta_rule_scan")
+                                       kv_heads, d_k, d_v, float(q_scale), float(unit_eps),
+                                       1 if decay_per_head else 0, _stream()), "delta_rule_scan")
+
+
+# --------------------------------------------------------------------------- routed feed-forward (mixture of experts)
+MAX_EXPERTS, MAX_EXPERTS_PER_TOKEN = 1024, 32   # moe.cu
+
+
+def moe_route(h: torch.Tensor, router: torch.Tensor, chosen: torch.Tensor, weights: torch.Tensor, n_groups: int,
+              keep_groups: int, norm_eps: float, scores: torch.Tensor | None = None) -> None:
+    """Per token of h [T, width]: softmax scores over router [E, width] (float32), the ``top`` = chosen.shape[1] best
+    experts among the ``keep_groups`` best of ``n_groups`` groups of neighbours into chosen int32 [T, top], and
+    their scores over the chosen scores' sum (+ norm_eps) into weights float32 [T, top]."""
+    _dev(h, router, chosen, weights, scores)
+    T, width = h.shape
+    E = router.shape[0]
+    assert router.dtype == torch.float32 and router.is_contiguous() and router.shape[1] == width and h.stride(1) == 1
+    assert chosen.dtype == torch.int32 and weights.dtype == torch.float32 and chosen.is_contiguous() and weights.is_contiguous()
+    assert chosen.shape == weights.shape and chosen.shape[0] == T
+    assert scores is None or (scores.dtype == torch.float32 and scores.is_contiguous() and tuple(scores.shape) == (T, E))
+    _check(_fn("b200_moe_route")(h.data_ptr(), h.stride(0), dtype_code(h.dtype), router.data_ptr(), chosen.data_ptr(),
+                                 weights.data_ptr(), scores.data_ptr() if scores is not None else None, T, width, E,
+                                 int(n_groups), int(keep_groups), chosen.shape[1], float(norm_eps), _stream()), "moe_route")
+
+
+def moe_experts(h: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, chosen: torch.Tensor, weights: torch.Tensor,
+                y: torch.Tensor, residual: torch.Tensor, activation: str, gate_args=(0.0, 0.0)) -> None:
+    """residual[t] += sum_k weights[t, k] down_e( act(gate_e h[t], up_e h[t]) ), e = chosen[t, k]: every (token,
+    expert) pair as a weight-streaming product.  w_gate_up [E, 2 ff, width] (gate and up rows interleaved), w_down
+    [E, width, ff], y [T top, ff] scratch of h's dtype."""
+    _dev(h, w_gate_up, w_down, chosen, weights, y, residual)
+    T, width = h.shape
+    E, ff2, _ = w_gate_up.shape
+    top = chosen.shape[1]
+    assert h.dtype == w_gate_up.dtype == w_down.dtype == y.dtype and residual.dtype == torch.float32
+    assert w_gate_up.is_contiguous() and w_down.is_contiguous() and y.is_contiguous() and residual.is_contiguous()
+    assert tuple(w_down.shape) == (E, width, ff2 // 2) and tuple(y.shape) == (T * top, ff2 // 2) and h.stride(1) == 1
+    _check(_fn("b200_moe_experts")(h.data_ptr(), h.stride(0), dtype_code(h.dtype), w_gate_up.data_ptr(), w_down.data_ptr(),
+                                   chosen.data_ptr(), weights.data_ptr(), y.data_ptr(), residual.data_ptr(), T, width,
+                                   ff2 // 2, top, ACTIVATION_CODES[activation], float(gate_args[0]), float(gate_args[1]),
+                                   _stream()), "moe_experts")
+
+
+def moe_group(chosen: torch.Tensor, n_experts: int, offsets: torch.Tensor, order: torch.Tensor, place: torch.Tensor) -> None:
+    """Orders the (token, choice) pairs of chosen [T, top] by expert: offsets int32 [E + 1] (expert e's run),
+    order int32 [T top] (the pair at each place), place int32 [T top] (each pair's place)."""
+    _dev(chosen, offsets, order, place)
+    n = chosen.numel()
+    assert chosen.dtype == offsets.dtype == order.dtype == place.dtype == torch.int32
+    assert offsets.numel() == n_experts + 1 and order.numel() == n and place.numel() == n
+    _check(_fn("b200_moe_group")(chosen.data_ptr(), n, n_experts, offsets.data_ptr(), order.data_ptr(), place.data_ptr(),
+                                 _stream()), "moe_group")
+
+
+def moe_gather(h: torch.Tensor, order: torch.Tensor, out: torch.Tensor, top: int) -> None:
+    """out[p] = h[order[p] // top]: the inputs in the order of their experts."""
+    _dev(h, order, out)
+    assert h.dtype == out.dtype and out.is_contiguous() and h.stride(1) == 1 and out.shape[1] == h.shape[1]
+    _check(_fn("b200_moe_gather")(h.data_ptr(), h.stride(0), dtype_code(h.dtype), order.data_ptr(), out.data_ptr(),
+                                  out.shape[0], h.shape[1], top, _stream()), "moe_gather")
+
+
+def moe_combine(o: torch.Tensor, place: torch.Tensor, weights: torch.Tensor, residual: torch.Tensor) -> None:
+    """residual[t] += sum_k weights[t, k] o[place[t top + k]] (o float32 [T top, width])."""
+    _dev(o, place, weights, residual)
+    T, top = weights.shape
+    assert o.dtype == residual.dtype == weights.dtype == torch.float32 and o.is_contiguous() and residual.is_contiguous()
+    assert o.shape[0] == T * top and o.shape[1] == residual.shape[1] and residual.shape[0] == T
+    _check(_fn("b200_moe_combine")(o.data_ptr(), place.data_ptr(), weights.data_ptr(), residual.data_ptr(), T,
+                                   residual.shape[1], top, _stream()), "moe_combine")

@@ -11,11 +11,13 @@ from .block import PreNormBlock
 from .embedding import OutputHead, TokenEmbedding
 from .streams import ConnectedBlock, StreamConnection
 from .latent_attention import LatentAttention
-from .delta_rule import ChannelDeltaRule
+from .delta_rule import ChannelDeltaRule, HeadDeltaRule
+from .norm import LayerNorm
+from .routed_feed_forward import RoutedFeedForward
 
 __all__ = ["Block", "FeedForward", "Mixer", "Norm", "Part", "PartRegistryError", "PositionEncoding", "ScaledRows",
            "StepContext", "all_parts", "build_block", "build_part", "register_block", "register_feed_forward",
            "register_mixer", "register_norm", "register_part", "register_position_encoding", "registered", "unregister", "Linear", "RMSNorm", "NoPositionEncoding",
            "RotaryPositionEncoding", "llama3_inverse_frequencies", "GroupedQueryAttention", "SwiGLUFeedForward",
            "PreNormBlock", "OutputHead", "TokenEmbedding", "ConnectedBlock", "StreamConnection", "LatentAttention",
-           "ChannelDeltaRule"]
+           "ChannelDeltaRule", "HeadDeltaRule", "LayerNorm", "RoutedFeedForward"]

@@ -10,7 +10,16 @@ Further parameters, all off for Llama 3: biases of the three projections; an RMS
 query and key head; a score scale other than 1/sqrt(head size); a value size other than the key size; keys and values
 taken from the cache another layer writes (the mixer then has no key and value projections).  With any of them on, a
 kernel between the projection and the rotation finishes the heads (bias, norm, the scale folded into the queries) and
-widens them with zeros to one size the attention kernels take; the output product's columns are widened to match."""
+widens them with zeros to one size the attention kernels take; the output product's columns are widened to match.
+
+More parameters of the same kind: an RMS norm with weights over the whole query projection and the whole key
+projection, before they are split into heads (``projection_norm``); first positions that stay visible behind the window
+(``keep_first``: i sees j when j <= i and (i - j < window or j < keep_first)); a distance penalty slope_h (i - j) taken
+off every score with slope_h = 2^(-``distance_slope_base`` (h + 1) / heads); a learned number per head whose
+exponential joins the softmax's denominator (``sink``); values mixed with those the first such layer of the pass made
+for the same token, v <- (1 - l) v + l v_first with a learned l, the mixed values being what is cached (``value_mix``:
+``"source"`` for that first layer, ``"mixed"`` for the others); and a gate per head, sigmoid(W_g x), on the heads'
+outputs (``output_gate``)."""
 from __future__ import annotations
 
 import torch
@@ -30,16 +39,31 @@ class GroupedQueryAttention(Mixer):
     def __init__(self, hidden_size: int, n_heads: int, n_kv_heads: int, head_dim: int, position: PositionEncoding,
                  window: int | None = None, *, value_dim: int | None = None, bias: bool = False,
                  qk_norm_eps: float | None = None, scale: float | None = None, shares_cache: bool = False,
-                 cache_window="own"):
+                 cache_window="own", projection_norm: bool = False, keep_first: int = 0,
+                 distance_slope_base: float | None = None, sink: bool = False, value_mix: str | None = None,
+                 output_gate: bool = False):
         """``cache_window``: how many of the latest positions the cache entry keeps (``"own"``: this mixer's window);
         a layer whose cache other layers read with a longer window, or with none, is told so here."""
+        if value_mix not in (None, "source", "mixed"):
+            raise ConfigError(f"value_mix {value_mix!r}: None, 'source' or 'mixed'")
+        if projection_norm and qk_norm_eps is None:
+            raise ConfigError("projection_norm needs qk_norm_eps")
+        if keep_first < 0 or (keep_first and window is None):
+            raise ConfigError(f"keep_first {keep_first} needs a window (and cannot be negative)")
+        if (value_mix or output_gate or projection_norm) and shares_cache:
+            raise ConfigError("a mixer that reads another layer's cache has no values to mix, no gate and no weighted norm")
+        self.projection_norm, self.keep_first, self.sink = bool(projection_norm), int(keep_first), bool(sink)
+        self.distance_slope_base = float(distance_slope_base) if distance_slope_base is not None else None
+        self.value_mix, self.output_gate = value_mix, bool(output_gate)
+        # terms that only the attention kernels themselves can apply
+        self.has_terms = bool(self.keep_first or self.sink or self.distance_slope_base is not None or self.output_gate)
         if n_heads % n_kv_heads:
             raise ConfigError(f"n_heads {n_heads} must be a multiple of n_kv_heads {n_kv_heads}")
         self.key_dim, self.value_dim = int(head_dim), int(value_dim if value_dim is not None else head_dim)
         self.bias, self.qk_norm_eps, self.shares_cache = bool(bias), qk_norm_eps, bool(shares_cache)
         self.scale = float(scale) if scale is not None else None
         self.finishes_heads = bool(self.bias or qk_norm_eps is not None or scale is not None or shares_cache
-                                   or self.value_dim != self.key_dim
+                                   or self.value_dim != self.key_dim or value_mix or self.has_terms
                                    or (self.key_dim % ops.HEAD_DIM_STEP != 0 and not position.rotary_dim))
         if self.finishes_heads:
             if min(self.key_dim, self.value_dim) < 1:
@@ -76,13 +100,21 @@ class GroupedQueryAttention(Mixer):
         if self.bias:
             for n in ("q", "k", "v") if not self.shares_cache else ("q",):
                 p[n + "_bias"] = ParamSpec(p[n].shape[:1], "matrix")
+        if self.projection_norm:
+            p["q_norm"], p["k_norm"] = ParamSpec((H * dk,), "norm"), ParamSpec((G * dk,), "norm")
+        if self.sink:
+            p["sink"] = ParamSpec((H,), "normal", 0.0, 1.0)
+        if self.value_mix:
+            p["vmix"] = ParamSpec((), "normal", 0.5, 0.1)    # (the source layer's is stored too, and not used)
+        if self.output_gate:
+            p["g"] = ParamSpec((H, self.hidden_size))
         return p
 
     def children(self):
         return {"position": self.position}
 
     def cache_need(self):
-        return KVCacheNeed(self.n_kv_heads, self.head_dim, self.cache_window)
+        return KVCacheNeed(self.n_kv_heads, self.head_dim, self.cache_window, self.keep_first if self.cache_window else 0)
 
     def plan_decode(self, ctx: StepContext, cache: KVView) -> tuple[int, bool]:
         """How a decode step's attention is launched: into how many spans each sequence's keys are cut, and
@@ -108,8 +140,22 @@ class GroupedQueryAttention(Mixer):
         H, G, dk, dv, D = self.n_heads, self.n_kv_heads, self.key_dim, self.value_dim, self.head_dim
         names = ("q",) if self.shares_cache else ("q", "k", "v")
         mats = [tensors[n].to(device) for n in names]
+        if self.output_gate:
+            mats.append(tensors["g"].to(device))
         common = torch.float32 if (dtype == torch.float32 or any(m.dtype == torch.float32 for m in mats)) else mats[0].dtype
+        rows = sum(m.shape[0] for m in mats)
+        if rows % 8:   # the products' rows of 16-bit results start on 16-byte boundaries
+            mats.append(torch.zeros((8 - rows % 8, self.hidden_size), dtype=common, device=device))
         self.qkv = Linear(torch.cat([m.to(common) for m in mats], dim=0).contiguous())
+        self.value_off, self.gate_off = (H + G) * dk, (H + G) * dk + G * dv
+        f32 = lambda n: tensors[n].to(device=device, dtype=torch.float32).contiguous()
+        self.norm_weights = torch.cat([f32("q_norm"), f32("k_norm")]) if self.projection_norm else None
+        self.sinks = f32("sink") if self.sink else None
+        self.mix_weight = f32("vmix").reshape(1) if self.value_mix == "mixed" else None
+        self.slopes = None
+        if self.distance_slope_base is not None:
+            self.slopes = torch.tensor([2.0 ** (-self.distance_slope_base * (h + 1) / H) for h in range(H)],
+                                       dtype=torch.float64).to(device=device, dtype=torch.float32)
         o = tensors["o"].to(device)
         o = o.to(torch.float32 if dtype == torch.float32 else o.dtype)
         wide = torch.zeros((self.hidden_size, H, D), dtype=o.dtype, device=device)   # columns of the zeros behind a value head
@@ -119,16 +165,19 @@ class GroupedQueryAttention(Mixer):
             self.head_bias = torch.cat([tensors[n + "_bias"].to(device=device, dtype=torch.float32) for n in names]).contiguous()
         # the scale is folded into the queries: the attention kernels divide every score by sqrt(their head size)
         mul = (self.scale if self.scale is not None else dk ** -0.5) * D ** 0.5
-        norm = self.qk_norm_eps is not None
+        norm = 0 if self.qk_norm_eps is None else 2 if self.projection_norm else 1
+        wq, wk, per = (0, H * dk, True) if self.projection_norm else (-1, -1, False)
         b = (lambda off: off) if self.bias else (lambda off: -1)
         # without rotation the finished keys and values go straight into their cache pages; with it they go to the
         # dense rows that the rotation kernel reads
         direct = not self.position.rotary_dim
         keys, values = (ops.TO_CACHE_KEYS, ops.TO_CACHE_VALUES) if direct else (ops.TO_ROWS, ops.TO_ROWS)
-        segs = [ops.head_row_segment(0, H, dk, 0, D, b(0), norm, -1, mul)]
+        segs = [ops.head_row_segment(0, H, dk, 0, D, b(0), norm, wq, mul, weight_per_row=per)]
         if not self.shares_cache:
-            segs.append(ops.head_row_segment(H * dk, G, dk, H * D, D, b(H * dk), norm, target=keys))
-            segs.append(ops.head_row_segment((H + G) * dk, G, dv, (H + G) * D, D, b((H + G) * dk), target=values))
+            segs.append(ops.head_row_segment(H * dk, G, dk, H * D, D, b(H * dk), norm, wk, target=keys, weight_per_row=per))
+            # (mixed values: the other layer's rows are handed over as a view that starts at its values)
+            segs.append(ops.head_row_segment((H + G) * dk, G, dv, (H + G) * D, D, b((H + G) * dk), target=values,
+                                             mix_off=0 if self.value_mix == "mixed" else -1))
         self.segments = ops.head_row_segments(*segs)
         self.query_segment = ops.head_row_segments(segs[0])
         self.writes_direct = direct
@@ -143,14 +192,23 @@ class GroupedQueryAttention(Mixer):
         if self.finishes_heads:
             if writes_cache and self.shares_cache:
                 raise ConfigError("a mixer without key and value projections cannot write a cache entry")
-            raw = self.qkv.store(x, ctx.dtype, ctx.empty)
+            # (the rows of a layer whose values later layers mix with theirs outlive the block: they come from the allocator)
+            raw = self.qkv.store(x, ctx.dtype, ctx.empty if self.value_mix != "source" else None)
+            mix = None
+            if self.value_mix == "source":
+                ctx.extras[VALUE_MIX_SOURCE] = raw[:, self.value_off:self.value_off + self.n_kv_heads * self.value_dim]
+            elif self.value_mix == "mixed":
+                if VALUE_MIX_SOURCE not in ctx.extras:
+                    raise ConfigError("a layer mixes its values with an earlier layer's, and no earlier layer of the pass left any")
+                mix = (ctx.extras[VALUE_MIX_SOURCE], self.mix_weight)
             if self.writes_direct:
                 qkv = ctx.empty((x.shape[0], self.q_dim), ctx.dtype)
                 ops.head_rows(raw, qkv, self.segments if writes_cache else self.query_segment, self.qk_norm_eps or 0.0,
-                              self.head_bias, cache=(ctx.positions, ctx.seq_ids, table, cache.k, cache.v) if writes_cache else None)
+                              self.head_bias, self.norm_weights, mix=mix if writes_cache else None,
+                              cache=(ctx.positions, ctx.seq_ids, table, cache.k, cache.v) if writes_cache else None)
             else:
                 qkv = ctx.empty((x.shape[0], self.q_dim + 2 * self.kv_dim), ctx.dtype)   # (a reader leaves the key and value columns unused)
-                ops.head_rows(raw, qkv, self.segments, self.qk_norm_eps or 0.0, self.head_bias)
+                ops.head_rows(raw, qkv, self.segments, self.qk_norm_eps or 0.0, self.head_bias, self.norm_weights, mix=mix)
                 ops.rope_cache_write(qkv, ctx.positions, ctx.seq_ids, table, self.position.inverse_frequencies(x.device),
                                      cache.k, cache.v, self.n_heads, self.n_kv_heads, self.head_dim,
                                      self.position.rotary_dim, self.position.pairing, write_cache=writes_cache)
@@ -170,13 +228,19 @@ class GroupedQueryAttention(Mixer):
                 ops.rope_cache_write(qkv, ctx.positions, ctx.seq_ids, table, self.position.inverse_frequencies(x.device),
                                      cache.k, cache.v, self.n_heads, self.n_kv_heads, self.head_dim,
                                      self.position.rotary_dim, self.position.pairing, write_cache=writes_cache)
-        if not attended and not fast.try_attention(qkv, out, ctx, table, cache, self):
+        gate = raw[:, self.gate_off:self.gate_off + self.n_heads] if self.output_gate else None
+        if not attended and not fast.try_attention(qkv, out, ctx, table, cache, self, gate):
             # (the plain kernel: a step of few tokens cuts their keys into spans so that the GPU has CTAs to run)
             rows = x.shape[0] * self.n_heads
-            splits = 1 if rows >= 1024 else max(1, min(16, 1024 // rows, ctx.capacity(cache.group) // 512))
+            reach = ctx.capacity(cache.group) if not self.window else min(ctx.capacity(cache.group), self.window + self.keep_first)
+            splits = 1 if rows >= 1024 else max(1, min(16, 1024 // rows, reach // 512))
             ops.attention_paged(qkv, qkv.shape[1], out, ctx.positions, ctx.seq_ids, table, cache.k, cache.v,
-                                self.n_heads, self.n_kv_heads, self.head_dim, self.window or 0, n_splits=splits)
+                                self.n_heads, self.n_kv_heads, self.head_dim, self.window or 0, n_splits=splits,
+                                keep_first=self.keep_first, slopes=self.slopes, sinks=self.sinks, gate=gate)
         return self.o.add_to(out, residual, then_norm)
+
+
+VALUE_MIX_SOURCE = "value mix source"   # in a pass's ``ctx.extras``: the first value-mixing layer's own values [T, G dv]
 
 
 def kernel_head_dim(d: int) -> int:

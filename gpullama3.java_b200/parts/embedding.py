@@ -18,8 +18,10 @@ class TokenEmbedding(Part):
     graph_safe = True
     pad_safe = True
 
-    def __init__(self, vocab_size: int, hidden_size: int):
-        self.vocab_size, self.hidden_size = vocab_size, hidden_size
+    def __init__(self, vocab_size: int, hidden_size: int, scale: float = 1.0):
+        """``scale``: what every row is multiplied with on its way into the residual stream (the table itself, which a
+        tied output head reads, stays as stored)."""
+        self.vocab_size, self.hidden_size, self.scale = vocab_size, hidden_size, float(scale)
         self.table: torch.Tensor | None = None
 
     def parameters(self):
@@ -32,7 +34,7 @@ class TokenEmbedding(Part):
     def forward(self, tokens: torch.Tensor, alloc=None) -> torch.Tensor:
         shape = (tokens.numel(), self.hidden_size)
         out = alloc(shape, torch.float32) if alloc is not None else torch.empty(shape, dtype=torch.float32, device=tokens.device)
-        ops.embed_gather(self.table, tokens, out)
+        ops.embed_gather(self.table, tokens, out, self.scale)
         return out
 
 

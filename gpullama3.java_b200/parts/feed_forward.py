@@ -18,11 +18,17 @@ class SwiGLUFeedForward(FeedForward):
     graph_safe = True
     pad_safe = True
 
-    def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "silu"):
-        """``activation`` of the gate: ``silu`` (SwiGLU) or ``gelu_tanh`` (GELU in its tanh form)."""
+    def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "silu", limit: float | None = None,
+                 slope: float = 1.0):
+        """``activation`` of the gate: ``silu`` (SwiGLU), ``gelu_tanh`` (GELU in its tanh form), or
+        ``clamped_sigmoid``: with g = min(gate, limit) and u = clamp(up, -limit, limit) the unit's value is
+        g sigmoid(slope g) (u + 1)."""
         if activation not in ops.ACTIVATION_CODES:
             raise ConfigError(f"feed-forward activation {activation!r}; known: {', '.join(sorted(ops.ACTIVATION_CODES))}")
+        if activation == "clamped_sigmoid" and (limit is None or not limit > 0):
+            raise ConfigError(f"the clamped feed-forward needs a positive limit, got {limit!r}")
         self.hidden_size, self.intermediate_size, self.activation = hidden_size, intermediate_size, activation
+        self.gate_args = (float(limit or 0.0), float(slope))
         self.gate_up: Linear | None = None
         self.down: Linear | None = None
 
@@ -42,7 +48,7 @@ class SwiGLUFeedForward(FeedForward):
         return ctx.all_decode and self.activation == "silu" and self.gate_up.links_with(ctx.n_tokens, ctx.dtype)
 
     def forward(self, x, ctx: StepContext, residual, then_norm=None):
-        h = self.gate_up.gated(x, ctx.dtype, ctx.empty, self.activation)  # [T, intermediate]
+        h = self.gate_up.gated(x, ctx.dtype, ctx.empty, self.activation, self.gate_args)  # [T, intermediate]
         return self.down.add_to(h, residual, then_norm)
 
 

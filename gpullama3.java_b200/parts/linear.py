@@ -17,13 +17,13 @@ class Linear:
         self.weight = weight
         self.out_features, self.in_features = weight.shape
 
-    def _run(self, a, c: torch.Tensor, epilogue: int) -> None:
+    def _run(self, a, c: torch.Tensor, epilogue: int, gate_args=(0.0, 0.0)) -> None:
         if isinstance(a, ScaledRows):  # only handed to a product that said it links (links_with)
             ops.gemm_decode_linked(a.data, self.weight, c, epilogue, row_factors=(a.partials, a.eps, a.dim))
             return
-        if fast.try_gemm(a, self.weight, c, epilogue):
+        if fast.try_gemm(a, self.weight, c, epilogue, gate_args):
             return
-        ops.gemm_generic(a, self.weight, c, epilogue)
+        ops.gemm_generic(a, self.weight, c, epilogue, gate_args)
 
     def links_with(self, n_rows: int, dtype: torch.dtype) -> bool:
         """Whether this product can be one half of a split norm for ``n_rows`` rows of ``dtype``."""
@@ -55,14 +55,20 @@ class Linear:
         self._run(a, residual, ops.EPILOGUE_RESIDUAL_ADD)
         return None
 
+    def gated_into(self, a: torch.Tensor, c: torch.Tensor, activation: str = "silu", gate_args=(0.0, 0.0)) -> None:
+        """``gated`` into a tensor the caller brings."""
+        self._run(a, c, ops.GATED_EPILOGUE_OF[activation], gate_args)
+
     def gated_silu(self, a: torch.Tensor, out_dtype: torch.dtype, alloc=None) -> torch.Tensor:
         """W holds gate and up rows interleaved; returns silu(gate) * up as [T, out/2]."""
         return self.gated(a, out_dtype, alloc, "silu")
 
-    def gated(self, a: torch.Tensor, out_dtype: torch.dtype, alloc=None, activation: str = "silu") -> torch.Tensor:
+    def gated(self, a: torch.Tensor, out_dtype: torch.dtype, alloc=None, activation: str = "silu",
+              gate_args=(0.0, 0.0)) -> torch.Tensor:
         """W holds gate and up rows interleaved; returns act(gate) * up as [T, out/2] (``activation``: ``silu`` or
-        ``gelu_tanh``), the activation applied in the product's epilogue."""
+        ``gelu_tanh``), or with ``clamped_sigmoid`` g' sigmoid(slope g') (u' + 1) of the clamped pair (``gate_args`` =
+        (limit, slope)); all applied in the product's epilogue."""
         shape = (a.shape[0], self.out_features // 2)
         c = alloc(shape, out_dtype) if alloc is not None else torch.empty(shape, dtype=out_dtype, device=a.device)
-        self._run(a, c, ops.EPILOGUE_GATED_SILU if activation == "silu" else ops.EPILOGUE_GATED_GELU_TANH)
+        self._run(a, c, ops.GATED_EPILOGUE_OF[activation], gate_args)
         return c

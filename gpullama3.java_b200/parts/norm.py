@@ -1,4 +1,4 @@
-"""RMSNorm, the only norm of the Llama 3 decoder (inference/InferenceCore.java:47-56 of the
+"""Norms over the rows of the residual stream.  RMSNorm, the only norm of the Llama 3 decoder (inference/InferenceCore.java:47-56 of the
 reference project): used before the mixer, before the feed-forward and before the output head."""
 from __future__ import annotations
 
@@ -40,4 +40,30 @@ class RMSNorm(Norm):
         return out
 
 
+class LayerNorm(Norm):
+    """(x - mean) / sqrt(variance + eps) * weight + bias over the residual stream's rows, the variance being the mean of
+    the squared deviations.  Weight and bias are kept, and applied, in 32 bits."""
+    graph_safe = True
+    pad_safe = True
+
+    def __init__(self, dim: int, eps: float):
+        self.dim, self.eps = int(dim), float(eps)
+        self.weight: torch.Tensor | None = None
+        self.bias: torch.Tensor | None = None
+
+    def parameters(self):
+        return {"weight": ParamSpec((self.dim,), "norm"), "bias": ParamSpec((self.dim,), "normal", 0.0, 0.02)}
+
+    def load(self, tensors, dtype, device):
+        self.weight = tensors["weight"].to(device=device, dtype=torch.float32).contiguous()
+        self.bias = tensors["bias"].to(device=device, dtype=torch.float32).contiguous()
+
+    def forward(self, x, out_dtype, rows=None, alloc=None):
+        n = x.shape[0] if rows is None else rows.numel()
+        out = alloc((n, self.dim), out_dtype) if alloc is not None else torch.empty((n, self.dim), dtype=out_dtype, device=x.device)
+        ops.layernorm(x, self.weight, self.bias, out, self.eps, rows)
+        return out
+
+
 register_norm("rmsnorm", RMSNorm)
+register_norm("layernorm", LayerNorm)

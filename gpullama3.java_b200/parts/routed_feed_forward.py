@@ -1,0 +1,106 @@
+"""A routed feed-forward (mixture of experts): every token runs through a few of many small gated feed-forwards.
+
+    z = W_r h (32-bit) ;  s = softmax(z) over all experts
+    the experts form ``groups`` equal groups of neighbours; a group's score is its best expert's; only experts of the
+    ``keep_groups`` best groups can be chosen; the ``top`` best of those are
+    y = sum over the chosen e of  s_e / (sum of the chosen s + 1e-20) * down_e( act(gate_e h, up_e h) )
+
+The router and the weights are 32-bit in both precisions.  A step of few tokens runs every (token, expert) pair as a
+weight-streaming product whose expert is read on the device, so a decode step's launches do not depend on the
+routing and can be recorded.  A prompt's pairs are ordered by expert, and every expert's rows are one product of the
+same kernels the dense feed-forward uses (gated epilogue included); the per-expert row counts come back to the host
+for that, which is why a prompt pass of this part is not replayed from a recording."""
+from __future__ import annotations
+
+import torch
+
+from ..config.base import ConfigError
+from ..kernels import ops
+from ..weights.loader import ParamSpec
+from .base import FeedForward, StepContext, register_feed_forward
+from .linear import Linear
+
+
+class RoutedFeedForward(FeedForward):
+    graph_safe = True    # (decode steps: the pair kernels read the routing from device memory)
+    pad_safe = False     # a prompt pass reads the experts' row counts on the host
+
+    def __init__(self, hidden_size: int, intermediate_size: int, n_experts: int, top: int, groups: int = 1,
+                 keep_groups: int | None = None, activation: str = "silu", limit: float | None = None, slope: float = 1.0,
+                 weight_eps: float = 1e-20):
+        keep_groups = groups if keep_groups is None else keep_groups
+        if activation not in ops.ACTIVATION_CODES:
+            raise ConfigError(f"feed-forward activation {activation!r}; known: {', '.join(sorted(ops.ACTIVATION_CODES))}")
+        if activation == "clamped_sigmoid" and (limit is None or not limit > 0):
+            raise ConfigError(f"the clamped feed-forward needs a positive limit, got {limit!r}")
+        if not (1 <= n_experts <= ops.MAX_EXPERTS) or not (1 <= top <= min(n_experts, ops.MAX_EXPERTS_PER_TOKEN)):
+            raise ConfigError(f"routed feed-forward: {top} of {n_experts} experts (at most {ops.MAX_EXPERTS_PER_TOKEN} of "
+                              f"{ops.MAX_EXPERTS})")
+        if groups < 1 or n_experts % groups or not (1 <= keep_groups <= groups):
+            raise ConfigError(f"routed feed-forward: {n_experts} experts do not form {groups} equal groups of which "
+                              f"{keep_groups} are kept")
+        if top > keep_groups * (n_experts // groups):
+            raise ConfigError(f"routed feed-forward: {top} experts cannot come from {keep_groups} groups of {n_experts // groups}")
+        self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
+        self.n_experts, self.top, self.groups, self.keep_groups = int(n_experts), int(top), int(groups), int(keep_groups)
+        self.activation, self.gate_args, self.weight_eps = activation, (float(limit or 0.0), float(slope)), float(weight_eps)
+
+    def parameters(self):
+        p = {"router": ParamSpec((self.n_experts, self.hidden_size))}
+        for e in range(self.n_experts):
+            p[f"e{e}.gate"] = ParamSpec((self.intermediate_size, self.hidden_size))
+            p[f"e{e}.up"] = ParamSpec((self.intermediate_size, self.hidden_size))
+            p[f"e{e}.down"] = ParamSpec((self.hidden_size, self.intermediate_size))
+        return p
+
+    def load(self, tensors, dtype, device):
+        run = torch.float32 if dtype == torch.float32 else torch.bfloat16
+        E, ff, h = self.n_experts, self.intermediate_size, self.hidden_size
+        self.router = tensors["router"].to(device=device, dtype=torch.float32).contiguous()
+        self.w_gate_up = torch.empty((E, 2 * ff, h), dtype=run, device=device)   # gate and up rows interleaved
+        self.w_down = torch.empty((E, h, ff), dtype=run, device=device)
+        for e in range(E):
+            self.w_gate_up[e, 0::2] = tensors[f"e{e}.gate"].to(device=device, dtype=run)
+            self.w_gate_up[e, 1::2] = tensors[f"e{e}.up"].to(device=device, dtype=run)
+            self.w_down[e] = tensors[f"e{e}.down"].to(device=device, dtype=run)
+        self.gate_up = [Linear(self.w_gate_up[e]) for e in range(E)]
+        self.down = [Linear(self.w_down[e]) for e in range(E)]
+
+    def route(self, x: torch.Tensor, ctx: StepContext, scores: torch.Tensor | None = None):
+        T = x.shape[0]
+        chosen = ctx.empty((T, self.top), torch.int32)
+        weights = ctx.empty((T, self.top), torch.float32)
+        ops.moe_route(x, self.router, chosen, weights, self.groups, self.keep_groups, self.weight_eps, scores)
+        return chosen, weights
+
+    def by_expert(self, ctx: StepContext, n_tokens: int) -> bool:
+        """Whether the step's pairs are ordered by expert and run as one product per expert (prompts), or pair by pair."""
+        pairs = n_tokens * self.top
+        return not ctx.all_decode and n_tokens > 64 and pairs >= 8 * self.n_experts or pairs > 65535
+
+    def forward(self, x, ctx: StepContext, residual, then_norm=None):
+        T = x.shape[0]
+        chosen, weights = self.route(x, ctx)
+        if not self.by_expert(ctx, T):
+            y = ctx.empty((T * self.top, self.intermediate_size), ctx.dtype)
+            ops.moe_experts(x, self.w_gate_up, self.w_down, chosen, weights, y, residual, self.activation, self.gate_args)
+            return None
+        pairs = T * self.top
+        offsets = ctx.empty((self.n_experts + 1,), torch.int32)
+        order, place = ctx.empty((pairs,), torch.int32), ctx.empty((pairs,), torch.int32)
+        ops.moe_group(chosen, self.n_experts, offsets, order, place)
+        bounds = offsets.tolist()                                   # (waits for the routing: the products' row counts)
+        xs = ctx.empty((pairs, self.hidden_size), ctx.dtype)
+        ops.moe_gather(x, order, xs, self.top)
+        y = ctx.empty((pairs, self.intermediate_size), ctx.dtype)
+        o = ctx.empty((pairs, self.hidden_size), torch.float32)
+        for e in range(self.n_experts):
+            lo, hi = bounds[e], bounds[e + 1]
+            if hi > lo:
+                self.gate_up[e].gated_into(xs[lo:hi], y[lo:hi], self.activation, self.gate_args)
+                self.down[e].into(y[lo:hi], o[lo:hi])
+        ops.moe_combine(o, place, weights, residual)
+        return None
+
+
+register_feed_forward("routed", RoutedFeedForward)

@@ -37,8 +37,8 @@ def test_part_specs_nest_under_any_key():
             register_part("test_family", "holder", Holder)
     finally:
         unregister("test_family", "holder")
-    with pytest.raises(PartRegistryError, match="unknown norm kind 'layernorm'; registered: rmsnorm"):
-        build_part(PartSpec("norm", "layernorm", {}))
+    with pytest.raises(PartRegistryError, match="unknown norm kind 'groupnorm'; registered: layernorm, rmsnorm"):
+        build_part(PartSpec("norm", "groupnorm", {}))
     with pytest.raises(PartRegistryError, match="unknown part family"):
         build_part(PartSpec("nothing", "x", {}))
 

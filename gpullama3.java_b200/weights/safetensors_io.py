@@ -109,7 +109,7 @@ def write_safetensors(path: str | Path, tensors: dict[str, torch.Tensor], metada
         f.write(blob)
         for name in order:
             t = tensors[name].detach().cpu().contiguous()
-            f.write(t.view(torch.uint8).reshape(-1).numpy().tobytes() if t.numel() else b"")
+            f.write(t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b"")   # (reshape first: a tensor without dimensions cannot be viewed as bytes)
 
 
 def open_model_files(model_dir: str | Path) -> dict[str, SafetensorsFile]:

@@ -105,8 +105,8 @@ def assert_logits(got: torch.Tensor, ref: torch.Tensor, dtype, what: str = "", r
     """float32: accumulation-order noise only, at every position.  bfloat16: the engine rounds activations between its
     kernels, the plain implementation does not round at all; what is allowed is a few roundings' worth relative to the
     largest logit.  With a routed feed-forward a bfloat16 run may choose another expert than the plain implementation
-    where two scores lie within rounding of each other, which moves that token's logits: up to one position in twelve
-    may then lie outside (never in float32, where the scores agree to six digits)."""
+    where two scores lie within rounding of each other, which moves that token's logits: up to one position in six (two
+    of a short run) may then lie outside (never in float32, where the scores agree to six digits)."""
     got = got.detach().to("cpu", torch.float64)
     ref = ref.detach().to("cpu", torch.float64)
     assert got.shape == ref.shape, f"{what}: shape {tuple(got.shape)} vs {tuple(ref.shape)}"
@@ -118,6 +118,6 @@ def assert_logits(got: torch.Tensor, ref: torch.Tensor, dtype, what: str = "", r
         return
     worst, mean = err.amax(dim=-1), err.mean(dim=-1)
     bad = (worst > 0.08 * scale) | (mean > 0.012 * scale)
-    allowed = (bad.numel() + 11) // 12 if routed else 0
+    allowed = max(2, bad.numel() // 6) if routed else 0
     assert int(bad.sum()) <= allowed, (f"{what}: {int(bad.sum())} of {bad.numel()} positions outside "
                                        f"(max err {float(err.max()):.3e}, scale {scale:.3e})")

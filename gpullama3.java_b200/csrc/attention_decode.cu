@@ -26,6 +26,12 @@
 // directly as a partial of its own (m = score, l = 1, o = v), so the cache is only ever read for
 // positions written by earlier steps.
 //
+// Further terms (DecodeTerms; all off for the Llama 3 decoder), the same as the plain kernel's: with a window the first
+// keep_first positions stay visible (their blocks of keys are walked ahead of the window's, and count in the span plan);
+// a distance penalty slopes[h] * (position - key) taken off every score; a sink per head, a key without a value whose
+// exponential joins the denominator (the first warp of a sequence's first span starts its running maximum and sum
+// at (sinks[h], 1)); a gate per (sequence, head): the output is multiplied by sigmoid(gate).
+//
 // Sizes: head_dim 32, 64, 96 or 128; group size (heads per kv head) <= 16.  Others are refused.
 #include "attention_decode_static.h"
 #include <cstdint>
@@ -72,6 +78,14 @@ __device__ __forceinline__ uint4 keep_first(uint4 v, int n) {
 
 // Partials in scratch: o [span][head][d] floats, then ml [span][head][2] floats, `span` counted over all sequences
 // (n_seqs x n_splits of them at most; sequence i's are prefix_i .. prefix_i + count_i - 1 of span_plan).
+struct DecodeTerms {
+    int keep_first;
+    const float* slopes;           // [n_heads] or null
+    const float* sinks;            // [n_heads] or null
+    const __nv_bfloat16* gate;     // [n_seqs][ld_gate], column h, or null
+    int ld_gate;
+};
+
 struct RopeArgs {            // what the fused variant needs beyond the plain one
     const float* inv_freq;   // [head_dim / 2]
     int pairing;             // 0: (2j, 2j+1); 1: (j, j + head_dim/2)
@@ -97,21 +111,24 @@ __device__ __forceinline__ float rotate_elem(const __nv_bfloat16* x, int d, int 
 // number, and the merge kernel evaluates the same plan.  Lengths are read before the dependency wait, like kv_lens[seq].
 constexpr int kSpanPlanMaxSeqs = 64;   // larger batches (whose grids fill the GPU with one or two spans) keep equal counts
 
-__device__ __forceinline__ int cached_blocks(const int* __restrict__ kv_lens, int i, int window, bool own_key_apart) {
+__device__ __forceinline__ int cached_blocks(const int* __restrict__ kv_lens, int i, int window, bool own_key_apart,
+                                             int keep_first) {
     const int kv_len = kv_lens[i];
     const int lo = window > 0 ? max(0, kv_len - window) : 0;
     const int n_cached = own_key_apart ? kv_len - 1 : kv_len;
-    return n_cached > lo ? (n_cached - 1) / 32 - lo / 32 + 1 : 0;
+    const int n_keep = min(keep_first, lo);      // kept first positions the window no longer covers
+    return (n_cached > lo ? (n_cached - 1) / 32 - lo / 32 + 1 : 0) + (n_keep + 31) / 32;
 }
 
 // prefix and count of sequence `seq` (find_cta < 0), or of the sequence that owns CTA number `find_cta`; false if that
 // CTA is left over (the counts are rounded down, so up to n_seqs CTAs of a kv head may be)
 __device__ __forceinline__ bool span_plan(const int* __restrict__ kv_lens, int n_seqs, int n_splits, int window,
-                                          bool own_key_apart, int seq, int find_cta, int& owner, int& prefix, int& count) {
+                                          bool own_key_apart, int keep_first, int seq, int find_cta, int& owner, int& prefix,
+                                          int& count) {
     bool planned = n_splits > 1 && n_seqs <= kSpanPlanMaxSeqs;
     unsigned int total = 0;
     if (planned) {
-        for (int i = 0; i < n_seqs; ++i) total += (unsigned int)cached_blocks(kv_lens, i, window, own_key_apart);
+        for (int i = 0; i < n_seqs; ++i) total += (unsigned int)cached_blocks(kv_lens, i, window, own_key_apart, keep_first);
         planned = total > 0 && total < (1u << 20);   // (the products below stay inside 32 bits)
     }
     if (!planned) {
@@ -124,7 +141,7 @@ __device__ __forceinline__ bool span_plan(const int* __restrict__ kv_lens, int n
     int at = 0;
     bool found = false;
     for (int i = 0; i < n_seqs; ++i) {
-        const int c = 1 + (int)((unsigned int)cached_blocks(kv_lens, i, window, own_key_apart) * spare / total);
+        const int c = 1 + (int)((unsigned int)cached_blocks(kv_lens, i, window, own_key_apart, keep_first) * spare / total);
         if (find_cta < 0 ? i == seq : (find_cta >= at && find_cta < at + c)) {
             owner = i; prefix = at; count = c; found = true;
         }
@@ -141,7 +158,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, _
                         const int* __restrict__ kv_lens, const int* __restrict__ page_table, int table_stride,
                         __nv_bfloat16* __restrict__ k_pool, __nv_bfloat16* __restrict__ v_pool,
                         float* __restrict__ part_o, float* __restrict__ part_ml, int n_heads, int n_kv_heads,
-                        int window, int n_splits, RopeArgs rope) {
+                        int window, int n_splits, RopeArgs rope, DecodeTerms terms) {
     constexpr int D = KB * 32;
     constexpr int NJ = D / 8;  // output tiles of 8 dims
     constexpr int SLOTS = kAttnDecodeWarps + (FUSED ? 1 : 0);  // partials merged per CTA: the warps, and the new key
@@ -165,7 +182,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, _
     // before the wait for the predecessor; the queries, the step's key and value and the cache are read after it.
     // Which sequence this CTA works for, as which of its spans, and how many spans that sequence has:
     int seq, span_first, span_count;
-    if (!span_plan(kv_lens, (int)gridDim.z, n_splits, window, FUSED && rope.write_cache, -1,
+    if (!span_plan(kv_lens, (int)gridDim.z, n_splits, window, FUSED && rope.write_cache, terms.keep_first, -1,
                    (int)(blockIdx.z * gridDim.x + blockIdx.x), seq, span_first, span_count)) {
         pdl_wait();   // (a CTA that is left over; it still waits, so that this kernel's end implies its predecessor's)
         return;
@@ -175,15 +192,22 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, _
     const int lo = window > 0 ? max(0, kv_len - window) : 0;
     // keys read from the cache: all of them, or all but the step's own when this kernel writes that one
     const int n_cached = (FUSED && rope.write_cache) ? kv_len - 1 : kv_len;
+    // The blocks of 32 keys this sequence reads, numbered 0 .. n_blocks - 1: first those of the kept first positions the
+    // window no longer covers (keys below n_keep), then the window's (number v stands for block v + shift).  A block that
+    // holds kept keys and the window's first keys is walked twice, each key valid in one of the two.
+    const int n_keep = min(terms.keep_first, lo), kept_blocks = (n_keep + 31) / 32;
     const int first_block = lo / 32, last_block = n_cached > lo ? (n_cached - 1) / 32 : first_block - 1;
-    const int per_split = max(1, (last_block - first_block + 1 + span_count - 1) / span_count);
-    const int blk_begin = first_block + split * per_split;
-    const int blk_end = min(blk_begin + per_split, last_block + 1);
+    const int shift = first_block - kept_blocks;
+    const int n_blocks = kept_blocks + last_block - first_block + 1;
+    const int per_split = max(1, (n_blocks + span_count - 1) / span_count);
+    const int blk_begin = split * per_split;
+    const int blk_end = min(blk_begin + per_split, n_blocks);
+    auto block_of = [&](int v) { return v < kept_blocks ? v : v + shift; };
     const int* pages = page_table + (size_t)seq * table_stride;
     const size_t page_stride = (size_t)n_kv_heads * kPageTokens * D;
     const size_t head_off = (size_t)kvh * kPageTokens * D;
 
-    const int first_page = blk_begin + warp < blk_end ? pages[(blk_begin + warp) * 32 / kPageTokens] : 0;
+    const int first_page = blk_begin + warp < blk_end ? pages[block_of(blk_begin + warp) * 32 / kPageTokens] : 0;
     if (FUSED) {
         // The angles of the step's position, once per CTA and before the wait (they need only the length and the
         // frequencies): a lane that evaluated the sines and cosines of its own sixteen dimensions spent more
@@ -249,13 +273,25 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, _
 #pragma unroll
         for (int i = 0; i < 4; ++i) o[j][i] = 0.f;
     float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;  // rows g and g + 8; l is this lane's share
+    float slope_lo = 0.f, slope_hi = 0.f;
+    if (terms.slopes) {
+        slope_lo = g < group ? terms.slopes[kvh * group + g] : 0.f;
+        if (HI) slope_hi = g + 8 < group ? terms.slopes[kvh * group + g + 8] : 0.f;
+    }
+    if (terms.sinks && split == 0 && warp == 0) {   // the sink counts once per (sequence, head)
+        if (g < group) { m_lo = terms.sinks[kvh * group + g]; l_lo = t == 0 ? 1.f : 0.f; }
+        if (HI && g + 8 < group) { m_hi = terms.sinks[kvh * group + g + 8]; l_hi = t == 0 ? 1.f : 0.f; }
+    }
+    const int q_pos = kv_len - 1;
     // scores are scaled by a multiplication: a division by sqrt(d) that is no power of two (head sizes 32, 96, 128) is a
     // subroutine that, with this kernel's registers all taken, cost more than the block's tensor-core work
     const float inv_sqrt_d = 1.f / sqrtf((float)D);
 
-    for (int blk = blk_begin + warp; blk < blk_end; blk += kAttnDecodeWarps) {
-        const int base = blk * 32;
-        const size_t page_base = (size_t)(blk == blk_begin + warp ? first_page : pages[base / kPageTokens]) * page_stride + head_off;
+    for (int vblk = blk_begin + warp; vblk < blk_end; vblk += kAttnDecodeWarps) {
+        const int base = block_of(vblk) * 32;
+        const bool kept = vblk < kept_blocks;
+        const int key_lo = kept ? 0 : lo, key_end = kept ? n_keep : n_cached;    // the block's valid keys lie in [key_lo, key_end)
+        const size_t page_base = (size_t)(vblk == blk_begin + warp ? first_page : pages[base / kPageTokens]) * page_stride + head_off;
         const int in_page = base % kPageTokens;
         const __nv_bfloat16* kp = k_pool + page_base;
         const __nv_bfloat16* vp = v_pool + page_base;
@@ -296,11 +332,12 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, _
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const int key = base + 8 * t + 2 * i + e;
-                const bool ok = key >= lo && key < n_cached;
-                s[i][e] = ok ? s[i][e] * inv_sqrt_d : -INFINITY;
+                const bool ok = key >= key_lo && key < key_end;
+                const float dist = (float)(q_pos - key);
+                s[i][e] = ok ? s[i][e] * inv_sqrt_d - slope_lo * dist : -INFINITY;
                 bm_lo = fmaxf(bm_lo, s[i][e]);
                 if (HI) {
-                    s[i][2 + e] = ok ? s[i][2 + e] * inv_sqrt_d : -INFINITY;
+                    s[i][2 + e] = ok ? s[i][2 + e] * inv_sqrt_d - slope_hi * dist : -INFINITY;
                     bm_hi = fmaxf(bm_hi, s[i][2 + e]);
                 }
             }
@@ -311,7 +348,8 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, _
             bm_hi = fmaxf(bm_hi, __shfl_xor_sync(0xffffffffu, bm_hi, 2));
         }
         const float mn_lo = fmaxf(m_lo, bm_lo), mn_hi = HI ? fmaxf(m_hi, bm_hi) : 0.f;
-        // a block always holds at least one valid key (blocks run from lo/32 to (n_cached-1)/32), so mn is finite
+        // a block always holds at least one valid key (blocks run from lo/32 to (n_cached-1)/32, kept ones from 0 to
+        // (n_keep-1)/32), so mn is finite
         const float c_lo = expf(m_lo - mn_lo), c_hi = HI ? expf(m_hi - mn_hi) : 0.f;
         m_lo = mn_lo;
         m_hi = mn_hi;
@@ -335,7 +373,9 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, _
                 pa[i][1] = pack_bf16(p2, p3);
             }
         }
-        const int n_valid = n_cached - (base + 8 * t);  // keys of this lane's V slice that exist
+        // keys of this lane's V slice that hold values of this sequence (a probability of zero times a stale value that is
+        // not finite would be NaN); kept blocks lie wholly below the sequence's length
+        const int n_valid = (kept ? n_cached : key_end) - (base + 8 * t);
 #pragma unroll
         for (int j = 0; j < NJ; ++j) {
             const uint4 v = n_valid >= 8 ? vf[j] : keep_first(vf[j], max(n_valid, 0));
@@ -442,6 +482,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, _
         }
         const int head = kvh * group + row;
         if (n_splits == 1) {
+            if (terms.gate) acc *= 1.0f / (1.0f + expf(-__bfloat162float(terms.gate[(size_t)seq * terms.ld_gate + head])));
             out[((size_t)seq * n_heads + head) * D + d] = __float2bfloat16_rn(acc / l);
         } else {
             const size_t p = (size_t)(span_first + split) * n_heads + head;
@@ -455,7 +496,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, _
 template <int N>
 __device__ __forceinline__ void merge_spans_at_once(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                                     __nv_bfloat16* __restrict__ out, size_t row, size_t first, size_t stride,
-                                                    int count, int D) {
+                                                    int count, int D, float gate) {
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
         float ms[N], ls[N], po[N];
 #pragma unroll
@@ -478,7 +519,7 @@ __device__ __forceinline__ void merge_spans_at_once(const float* __restrict__ pa
                 acc += po[j] * f;
             }
         }
-        out[row * D + d] = __float2bfloat16_rn(acc / l);
+        out[row * D + d] = __float2bfloat16_rn(acc / l * gate);
     }
 }
 
@@ -488,18 +529,20 @@ __device__ __forceinline__ void merge_spans_at_once(const float* __restrict__ pa
 // pays one round trip to L2 per span); they are added in span order, so the sum is the same.
 __global__ void attention_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                               __nv_bfloat16* __restrict__ out, const int* __restrict__ kv_lens, int n_heads,
-                                              int n_splits, int D, int window, int own_key_apart) {
+                                              int n_splits, int D, int window, int own_key_apart, int keep_first,
+                                              const __nv_bfloat16* __restrict__ gate, int ld_gate) {
     pdl_launch_dependents();
     const size_t row = blockIdx.x;  // seq * n_heads + head
     const int seq = (int)(blockIdx.x / n_heads), head = (int)(blockIdx.x % n_heads);
     int owner, span_first, count;
-    span_plan(kv_lens, (int)(gridDim.x / n_heads), n_splits, window, own_key_apart != 0, seq, -1, owner, span_first, count);
+    span_plan(kv_lens, (int)(gridDim.x / n_heads), n_splits, window, own_key_apart != 0, keep_first, seq, -1, owner, span_first, count);
     pdl_wait();
+    const float gv = gate ? 1.0f / (1.0f + expf(-__bfloat162float(gate[(size_t)seq * ld_gate + head]))) : 1.f;
     const size_t first = (size_t)span_first * n_heads + head, stride = (size_t)n_heads;
     // up to 16 spans: everything a thread needs is asked for at once (one trip to L2 instead of one for the maxima and one
     // for the rest, per group of 8 spans); the arithmetic and its order are those of the general path below
-    if (count <= 8) { merge_spans_at_once<8>(part_o, part_ml, out, row, first, stride, count, D); return; }
-    if (count <= 16) { merge_spans_at_once<16>(part_o, part_ml, out, row, first, stride, count, D); return; }
+    if (count <= 8) { merge_spans_at_once<8>(part_o, part_ml, out, row, first, stride, count, D, gv); return; }
+    if (count <= 16) { merge_spans_at_once<16>(part_o, part_ml, out, row, first, stride, count, D, gv); return; }
     float m = -INFINITY;
     for (int s0 = 0; s0 < count; s0 += 8) {
         float ms[8];
@@ -530,7 +573,7 @@ __global__ void attention_decode_merge_kernel(const float* __restrict__ part_o, 
                 }
             }
         }
-        out[row * D + d] = __float2bfloat16_rn(acc / l);
+        out[row * D + d] = __float2bfloat16_rn(acc / l * gv);
     }
 }
 
@@ -547,8 +590,10 @@ namespace b200 {
 static int launch_attention_decode(const void* q, int q_row_stride, void* out, const int* kv_lens, const int* page_table,
                                    int table_stride, void* k_pool, void* v_pool, float* scratch, long long scratch_floats,
                                    int n_seqs, int n_heads, int n_kv_heads, int head_dim, int window, int n_splits,
-                                   bool fused, RopeArgs rope, bool early_start, cudaStream_t stream) {
+                                   bool fused, RopeArgs rope, bool early_start, cudaStream_t stream,
+                                   DecodeTerms terms = DecodeTerms{0, nullptr, nullptr, nullptr, 0}) {
     if (n_seqs <= 0) return 0;
+    if (terms.keep_first < 0 || (terms.keep_first > 0 && window <= 0)) return kErrBadArgument;
     if (n_kv_heads <= 0 || n_heads % n_kv_heads != 0 || n_splits < 1) return kErrBadArgument;
     const int group = n_heads / n_kv_heads;
     if (group > 16 || head_dim % 32 != 0 || head_dim < 32 || head_dim > 128 || q_row_stride % 8 != 0) return kErrUnsupportedSize;
@@ -583,7 +628,7 @@ static int launch_attention_decode(const void* q, int q_row_stride, void* out, c
         }                                                                                                           \
         st = launch_pdl_cluster(kernel, grid, dim3(kAttnDecodeThreads), smem, stream, dim3(1, 1, 1), early_start, qq,   \
                                 q_row_stride, oo, kv_lens, page_table, table_stride, kk, vv, part_o, part_ml, n_heads,  \
-                                n_kv_heads, window, n_splits, rope);                                                 \
+                                n_kv_heads, window, n_splits, rope, terms);                                          \
     } while (0)
 #define B200_PICK(KB) do { if (fused) B200_LAUNCH(KB, true); else B200_LAUNCH(KB, false); } while (0)
     switch (head_dim / 32) {
@@ -598,7 +643,7 @@ static int launch_attention_decode(const void* q, int q_row_stride, void* out, c
     if (st != 0 || n_splits == 1) return st;
     return launch_pdl(attention_decode_merge_kernel, dim3(n_seqs * n_heads), dim3(head_dim <= 64 ? 64 : 128), 0, stream,
                       (const float*)part_o, (const float*)part_ml, oo, kv_lens, n_heads, n_splits, head_dim, window,
-                      (fused && rope.write_cache) ? 1 : 0);
+                      (fused && rope.write_cache) ? 1 : 0, terms.keep_first, terms.gate, terms.ld_gate);
 }
 
 }  // namespace b200
@@ -645,6 +690,19 @@ extern "C" int b200_attention_decode(const void* q, int q_row_stride, void* out,
     return b200::launch_attention_decode(q, q_row_stride, out, kv_lens, page_table, table_stride, const_cast<void*>(k_pool),
                                          const_cast<void*>(v_pool), scratch, scratch_floats, n_seqs, n_heads, n_kv_heads,
                                          head_dim, window, n_splits, false, b200::RopeArgs{nullptr, 0, 0}, early_start != 0, stream);
+}
+
+// The same with the further terms of DecodeTerms (null pointers and keep_first 0 switch each off).
+extern "C" int b200_attention_decode_terms(const void* q, int q_row_stride, void* out, const int* kv_lens,
+                                           const int* page_table, int table_stride, const void* k_pool, const void* v_pool,
+                                           float* scratch, long long scratch_floats, int n_seqs, int n_heads, int n_kv_heads,
+                                           int head_dim, int window, int n_splits, int early_start, int keep_first,
+                                           const float* slopes, const float* sinks, const void* gate, int ld_gate,
+                                           cudaStream_t stream) {
+    return b200::launch_attention_decode(q, q_row_stride, out, kv_lens, page_table, table_stride, const_cast<void*>(k_pool),
+                                         const_cast<void*>(v_pool), scratch, scratch_floats, n_seqs, n_heads, n_kv_heads,
+                                         head_dim, window, n_splits, false, b200::RopeArgs{nullptr, 0, 0}, early_start != 0, stream,
+                                         b200::DecodeTerms{keep_first, slopes, sinks, (const __nv_bfloat16*)gate, ld_gate});
 }
 
 // The fused variant: `qkv` holds the step's raw projections [n_seqs, (n_heads + 2 n_kv_heads) head_dim]; queries

@@ -11,10 +11,24 @@
 // order inside a block chosen so that the probabilities a lane holds after Q K^T are those of the
 // 8 consecutive keys its V^T load covers (same scheme as the decode kernel).
 //
+// Further terms (PrefillTerms; all off for the Llama 3 decoder), the same as the plain kernel's: with a window the first
+// keep_first positions stay visible (their blocks of keys are walked ahead of the window's); a distance penalty
+// slopes[h] * (position - key) taken off every score, in 32 bits; a sink per head whose exponential joins the
+// denominator (every row's running maximum and sum start at (sinks[h], 1)); a gate per (token, head): the output is
+// multiplied by sigmoid(gate).
+//
 // Sizes: head_dim 32, 64, 96, 128.  Each warp owns 32 query rows (head_dim <= 64) or 16.
 #include "common.cuh"
 
 namespace b200 {
+
+struct PrefillTerms {
+    int keep_first;
+    const float* slopes;           // [n_heads] or null
+    const float* sinks;            // [n_heads] or null
+    const __nv_bfloat16* gate;     // [T][ld_gate], column h, or null
+    int ld_gate;
+};
 
 constexpr int kPrefillWarps = 4;
 constexpr int kPrefillThreads = kPrefillWarps * 32;
@@ -50,7 +64,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, 
                          const int* __restrict__ cu_seqlens, const int* __restrict__ kv_lens,
                          const int* __restrict__ page_table, int table_stride,
                          const __nv_bfloat16* __restrict__ k_pool, const __nv_bfloat16* __restrict__ v_pool,
-                         int n_heads, int n_kv_heads, int window) {
+                         int n_heads, int n_kv_heads, int window, PrefillTerms terms) {
     constexpr int D = KB * 32, NJ = D / 8, TILE = kPrefillWarps * MT * 16;
     const int seq = blockIdx.z, head = blockIdx.y;
     const int tok0 = cu_seqlens[seq], q_len = cu_seqlens[seq + 1] - tok0;
@@ -95,11 +109,24 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, 
             for (int i = 0; i < 4; ++i) o[mt][j][i] = 0.f;
     }
     const float scale_log2 = 1.4426950408889634f / sqrtf((float)D);  // log2(e) / sqrt(d)
+    // scores stay in units of q.k until the exponential: the penalty per position and the sink are carried into them
+    const float slope_qk = terms.slopes ? terms.slopes[head] * sqrtf((float)D) : 0.f;
+    if (terms.sinks) {
+        const float sink_qk = terms.sinks[head] * sqrtf((float)D);
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+            m_run[mt][0] = m_run[mt][1] = sink_qk;
+            l_run[mt][0] = l_run[mt][1] = t == 0 ? 1.f : 0.f;    // (the four lanes of a row add their sums at the end)
+        }
+    }
 
     // keys this warp needs: from the window's start of its first row to its last row's position
     const int p_first = start + row0, p_last = start + min(row0 + MT * 16, q_len) - 1;
     const int k_lo = window > 0 ? max(0, p_first - window + 1) : 0;
-    for (int blk = k_lo / 32; blk <= p_last / 32; ++blk) {
+    // blocks of kept first positions that lie wholly before the window's first block come first
+    const int kept_blocks = min((terms.keep_first + 31) / 32, k_lo / 32), shift = k_lo / 32 - kept_blocks;
+    for (int vblk = 0; vblk <= p_last / 32 - shift; ++vblk) {
+        const int blk = vblk < kept_blocks ? vblk : vblk + shift;
         const int base = blk * 32;
         const size_t page_base = (size_t)pages[base / kPageTokens] * page_stride + head_off;
         const int in_page = base % kPageTokens;
@@ -118,7 +145,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, 
         for (int j = 0; j < NJ; ++j)
             vf[j] = __ldg(reinterpret_cast<const uint4*>(vp + (size_t)(8 * j + g) * kPageTokens + in_page + t * 8));
         // no masking is needed when every key of the block is visible to every row of the warp
-        const bool full = base + 31 <= p_first && (window <= 0 || base >= p_last - window + 1);
+        const bool full = base + 31 <= p_first && (window <= 0 || base >= p_last - window + 1 || base + 31 < terms.keep_first);
         const int n_valid = kv_len - (base + 8 * t);
         if (n_valid < 8) {
 #pragma unroll
@@ -147,9 +174,19 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, 
                         const int key = base + 8 * t + 2 * i + e;
 #pragma unroll
                         for (int r = 0; r < 2; ++r) {
-                            const bool ok = key <= pos[mt][r] && (window <= 0 || key > pos[mt][r] - window);
+                            const bool ok = key <= pos[mt][r] && (window <= 0 || key > pos[mt][r] - window || key < terms.keep_first);
                             if (!ok) s[i][2 * r + e] = -INFINITY;
                         }
+                    }
+            }
+            if (terms.slopes) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const int key = base + 8 * t + 2 * i + e;
+#pragma unroll
+                        for (int r = 0; r < 2; ++r) s[i][2 * r + e] -= slope_qk * (float)(pos[mt][r] - key);
                     }
             }
 #pragma unroll
@@ -207,6 +244,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, 
             l += __shfl_xor_sync(0xffffffffu, l, 2);
             if (qi[mt][r] < q_len) {
                 __nv_bfloat16* orow = out + ((size_t)(tok0 + qi[mt][r]) * n_heads + head) * D;
+                if (terms.gate)   // (folded into the divisor: out = o / l * sigmoid(gate))
+                    l *= 1.0f + expf(-__bfloat162float(terms.gate[(size_t)(tok0 + qi[mt][r]) * terms.ld_gate + head]));
 #pragma unroll
                 for (int j = 0; j < NJ; ++j)
                     *reinterpret_cast<uint32_t*>(orow + 8 * j + 2 * t) = pack2(o[mt][j][2 * r] / l, o[mt][j][2 * r + 1] / l);
@@ -219,9 +258,12 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, 
 extern "C" int b200_attention_prefill(const void* q, int q_row_stride, void* out, const int* cu_seqlens,
                                       const int* kv_lens, const int* page_table, int table_stride, const void* k_pool,
                                       const void* v_pool, int n_seqs, int max_q_len, int n_heads, int n_kv_heads,
-                                      int head_dim, int window, cudaStream_t stream) {
+                                      int head_dim, int window, int keep_first, const float* slopes, const float* sinks,
+                                      const void* gate, int ld_gate, cudaStream_t stream) {
     using namespace b200;
     if (n_seqs <= 0 || max_q_len <= 0) return 0;
+    if (keep_first < 0 || (keep_first > 0 && window <= 0)) return kErrBadArgument;
+    const PrefillTerms terms = {keep_first, slopes, sinks, (const __nv_bfloat16*)gate, ld_gate};
     if (n_kv_heads <= 0 || n_heads % n_kv_heads != 0) return kErrBadArgument;
     if (head_dim % 32 != 0 || head_dim < 32 || head_dim > 128 || q_row_stride % 8 != 0) return kErrUnsupportedSize;
     if (n_seqs > 65535 || n_heads > 65535) return kErrUnsupportedSize;
@@ -234,7 +276,7 @@ extern "C" int b200_attention_prefill(const void* q, int q_row_stride, void* out
     auto oo = (__nv_bfloat16*)out;
 #define B200_LAUNCH(KB, MT)                                                                                       \
     attention_prefill_kernel<KB, MT><<<grid, kPrefillThreads, 0, stream>>>(qq, q_row_stride, oo, cu_seqlens, kv_lens, \
-        page_table, table_stride, kk, vv, n_heads, n_kv_heads, window)
+        page_table, table_stride, kk, vv, n_heads, n_kv_heads, window, terms)
     switch (head_dim / 32) {
         case 1: B200_LAUNCH(1, 2); break;
         case 2: B200_LAUNCH(2, 2); break;

@@ -54,8 +54,23 @@ def try_decode_attention_with_rope(qkv, out, ctx, page_table, cache, mixer, writ
 
 
 def try_attention(qkv, out, ctx, page_table, cache, mixer, gate=None) -> bool:
-    if getattr(mixer, "has_terms", False):   # kept first positions, distance penalty, sink, output gate: the plain kernel
-        return False
+    if getattr(mixer, "has_terms", False):
+        # kept first positions, distance penalty, sink, output gate: the span kernel for decode steps, the flash kernel
+        # for prompts (the tcgen05 prompt kernel does not have these terms)
+        terms = dict(keep_first=mixer.keep_first, slopes=mixer.slopes, sinks=mixer.sinks, gate=gate)
+        if qkv.dtype != torch.bfloat16 or mixer.head_dim not in (32, 64, 96, 128):
+            return False
+        if ctx.all_decode and ops.attention_decode_supported(qkv.dtype, mixer.n_heads, mixer.n_kv_heads, mixer.head_dim):
+            splits, early = mixer.plan_decode(ctx, cache)
+            ops.attention_decode(qkv, qkv.shape[1], out, ctx.kv_lens, page_table, cache.k, cache.v, mixer.n_heads,
+                                 mixer.n_kv_heads, mixer.head_dim, mixer.window or 0, splits, early_start=early, **terms)
+            return True
+        if qkv.shape[1] % 8 or (qkv.data_ptr() & 15):
+            return False
+        ops.attention_prefill(qkv, qkv.shape[1], out, ctx.cu_seqlens, ctx.kv_lens, page_table, cache.k, cache.v,
+                              ctx.n_seqs, ctx.max_q_len, mixer.n_heads, mixer.n_kv_heads, mixer.head_dim,
+                              mixer.window or 0, **terms)
+        return True
     if ctx.all_decode and ops.attention_decode_supported(qkv.dtype, mixer.n_heads, mixer.n_kv_heads, mixer.head_dim):
         splits, early = mixer.plan_decode(ctx, cache)
         ops.attention_decode(qkv, qkv.shape[1], out, ctx.kv_lens, page_table, cache.k, cache.v, mixer.n_heads,

@@ -62,8 +62,12 @@ _SIGNATURES = {
     "b200_attention_decode": ("attention_decode", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                                    c_void_p, c_void_p, ctypes.c_longlong, c_int, c_int, c_int, c_int,
                                                    c_int, c_int, c_int]),
+    "b200_attention_decode_terms": ("attention_decode", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                                         c_void_p, c_void_p, ctypes.c_longlong, c_int, c_int, c_int, c_int,
+                                                         c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int]),
     "b200_attention_prefill": ("attention_prefill", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
-                                                     c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int]),
+                                                     c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                                     c_void_p, c_void_p, c_void_p, c_int]),
     "b200_attention_decode_rope": ("attention_decode", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                                         c_void_p, c_void_p, ctypes.c_longlong, c_int, c_int, c_int,
                                                         c_int, c_int, c_int, c_void_p, c_int, c_int, c_int]),
@@ -605,10 +609,13 @@ def attention_decode_rope(qkv: torch.Tensor, out: torch.Tensor, kv_lens: torch.T
 def attention_decode(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, kv_lens: torch.Tensor,
                      page_table: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, n_heads: int,
                      n_kv_heads: int, head_dim: int, window: int, n_splits: int,
-                     scratch: torch.Tensor | None = None, early_start: bool = True) -> None:
+                     scratch: torch.Tensor | None = None, early_start: bool = True, *, keep_first: int = 0,
+                     slopes: torch.Tensor | None = None, sinks: torch.Tensor | None = None,
+                     gate: torch.Tensor | None = None) -> None:
     """One query token per sequence (row i of q belongs to sequence i) over kv_lens[i] cached keys.
     ``scratch``: float32 workspace for the spans' partial results (allocated here when absent).
-    ``early_start``: see ``attention_decode_early_start``."""
+    ``early_start``: see ``attention_decode_early_start``.  ``keep_first``, ``slopes``, ``sinks``, ``gate``: as for
+    ``attention_paged``."""
     _dev(q, out, kv_lens, page_table, k_pool, v_pool)
     n_seqs = out.shape[0]
     assert q.dtype == out.dtype == k_pool.dtype == torch.bfloat16 and out.is_contiguous()
@@ -617,6 +624,19 @@ def attention_decode(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, kv_l
     need = n_seqs * n_heads * n_splits * (head_dim + 2) if n_splits > 1 else 0
     if need and (scratch is None or scratch.numel() < need):
         scratch = torch.empty(need, dtype=torch.float32, device=q.device)
+    if keep_first or slopes is not None or sinks is not None or gate is not None:
+        _dev(slopes, sinks, gate)
+        for t in (slopes, sinks):
+            assert t is None or (t.dtype == torch.float32 and t.is_contiguous() and t.numel() == n_heads)
+        assert gate is None or (gate.dtype == torch.bfloat16 and gate.stride(1) == 1 and gate.shape[1] >= n_heads)
+        ptr = lambda t: t.data_ptr() if t is not None else None
+        _check(_fn("b200_attention_decode_terms")(
+            q.data_ptr(), q_row_stride, out.data_ptr(), kv_lens.data_ptr(), page_table.data_ptr(), page_table.shape[1],
+            k_pool.data_ptr(), v_pool.data_ptr(), scratch.data_ptr() if need else None, scratch.numel() if need else 0,
+            n_seqs, n_heads, n_kv_heads, head_dim, int(window), n_splits, 1 if early_start else 0, int(keep_first),
+            ptr(slopes), ptr(sinks), ptr(gate), gate.stride(0) if gate is not None else 0, _stream()),
+            "attention_decode_terms" if early_start else "attention_decode_terms:late")
+        return
     _check(_fn("b200_attention_decode")(
         q.data_ptr(), q_row_stride, out.data_ptr(), kv_lens.data_ptr(), page_table.data_ptr(), page_table.shape[1],
         k_pool.data_ptr(), v_pool.data_ptr(), scratch.data_ptr() if need else None, scratch.numel() if need else 0,
@@ -626,17 +646,25 @@ def attention_decode(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, kv_l
 
 def attention_prefill(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, cu_seqlens: torch.Tensor,
                       kv_lens: torch.Tensor, page_table: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
-                      n_seqs: int, max_q_len: int, n_heads: int, n_kv_heads: int, head_dim: int, window: int) -> None:
+                      n_seqs: int, max_q_len: int, n_heads: int, n_kv_heads: int, head_dim: int, window: int, *,
+                      keep_first: int = 0, slopes: torch.Tensor | None = None, sinks: torch.Tensor | None = None,
+                      gate: torch.Tensor | None = None) -> None:
     """Causal attention of packed query tokens: sequence i owns rows cu_seqlens[i]..cu_seqlens[i+1],
-    which are its last positions (kv_lens[i] - q_len .. kv_lens[i] - 1); keys come from the cache."""
-    _dev(q, out, cu_seqlens, kv_lens, page_table, k_pool, v_pool)
+    which are its last positions (kv_lens[i] - q_len .. kv_lens[i] - 1); keys come from the cache.
+    ``keep_first``, ``slopes``, ``sinks``, ``gate``: as for ``attention_paged``."""
+    _dev(q, out, cu_seqlens, kv_lens, page_table, k_pool, v_pool, slopes, sinks, gate)
+    for t in (slopes, sinks):
+        assert t is None or (t.dtype == torch.float32 and t.is_contiguous() and t.numel() == n_heads)
+    assert gate is None or (gate.dtype == torch.bfloat16 and gate.stride(1) == 1 and gate.shape[1] >= n_heads)
+    ptr = lambda t: t.data_ptr() if t is not None else None
     assert q.dtype == out.dtype == k_pool.dtype == torch.bfloat16 and out.is_contiguous()
     assert tuple(k_pool.shape[1:]) == (n_kv_heads, PAGE_TOKENS, head_dim)
     assert tuple(v_pool.shape[1:]) == (n_kv_heads, head_dim, PAGE_TOKENS)
     _check(_fn("b200_attention_prefill")(
         q.data_ptr(), q_row_stride, out.data_ptr(), cu_seqlens.data_ptr(), kv_lens.data_ptr(), page_table.data_ptr(),
         page_table.shape[1], k_pool.data_ptr(), v_pool.data_ptr(), n_seqs, max_q_len, n_heads, n_kv_heads, head_dim,
-        int(window), _stream()), "attention_prefill")
+        int(window), int(keep_first), ptr(slopes), ptr(sinks), ptr(gate), gate.stride(0) if gate is not None else 0,
+        _stream()), "attention_prefill")
 
 
 def attention_prefill_tc(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, cu_seqlens: torch.Tensor,

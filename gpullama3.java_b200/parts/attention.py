@@ -90,6 +90,7 @@ class GroupedQueryAttention(Mixer):
         self.o: Linear | None = None
         self.head_bias = None
         self.segments = None
+        self.norm_weights = self.sinks = self.slopes = self.mix_weight = None
 
     def parameters(self):
         H, G, dk, dv = self.n_heads, self.n_kv_heads, self.key_dim, self.value_dim
@@ -123,7 +124,7 @@ class GroupedQueryAttention(Mixer):
         group's ``kv_capacity``: a recorded step is replayed until its page tables are outgrown)."""
         capacity = ctx.capacity(cache.group)
         if self.window:
-            capacity = min(capacity, self.window)
+            capacity = min(capacity, self.window + self.keep_first)
         resident = ops.resident_ctas(ctx.device, self.head_dim, self.n_heads // self.n_kv_heads)
         splits = ops.attention_decode_splits(ctx.n_seqs, self.n_kv_heads, capacity, resident)
         return splits, ops.attention_decode_early_start(ctx.n_seqs, self.n_kv_heads, capacity, splits)

@@ -2,7 +2,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--model 1b|3b|8b] [--dtype bfloat16|float32]
                     [--batch 8] [--context 4096] [--layers L] [--sizes all|none]
-    python bench.py --design guduzen [--design-sizes s,m]     (another workload, see the end of this text)
+    python bench.py --design guduzen|pekerax [--design-sizes s,m]     (another workload, see the end of this text)
 
 Default run: the Llama-3.2-1B shape (BASELINE.json configs[2]) with random bfloat16 weights, a
 batch of 8 sequences at context length 4096.  A "step" is one decode step.  ``value`` is decoded
@@ -24,6 +24,12 @@ project); here the prompt step and the decode steps are timed apart, on the devi
 attention, attention reading that layer's cache, latent attention, delta rule; three residual streams) beside a Llama 3
 decoder of the same width, depth, heads and vocabulary at two sizes: a prompt of 2,048 tokens, decode steps at
 ``--batch`` and a context of 2,048, and the device time of every kernel function in one prompt pass and one decode step.
+
+``--design pekerax`` does the same for the Pekerax decoder (layers in the order delta rule, attention, attention; the
+attention with kept first positions, distance penalty, sink, value mixing and output gate; the first feed-forward dense,
+the others routed: 8 experts of half the dense width, 2 per token) beside the Guduzen decoder, the closest existing
+model (window attention, delta rule, dense gated feed-forward), and the Llama 3 decoder, all of equal width, depth and
+heads.
 
 The library runs on one GPU: for --gpus N > 1 it says so and exits with 2.
 """
@@ -415,6 +421,21 @@ def guduzen_config(z):
             "norm": {"eps": 1e-6}, "layers": layers}
 
 
+def pekerax_config(z):
+    """Layers in the order delta rule, attention, attention, repeated; the first layer's feed-forward dense, the others
+    routed (8 experts of half the dense width, 2 per token: the same products per token as the dense one)."""
+    att = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"], "scale": z["dim"] ** -0.5,
+           "mask": {"size": z["window"], "keep_first": 4}, "v_mix": True}
+    delta = {"heads": z["heads"], "kv_heads": z["heads"], "dim": z["dim"], "vdim": z["dim"], "conv": 4}
+    dense = {"kind": "dense", "ff": z["ff"], "limit": 7.0}
+    moe = {"kind": "moe", "expert": {"ff": z["ff"] // 2, "limit": 7.0},
+           "router": {"experts": 8, "top": 2, "groups": {"count": 4, "keep": 2}}}
+    layers = [{"type": "delta" if i % 3 == 0 else "attention", "mixer": dict(delta if i % 3 == 0 else att),
+               "mlp": dense if i == 0 else moe} for i in range(z["layers"])]
+    return {"architecture": "Pekerax", "vocab": z["vocab"], "width": z["width"], "embedding": {"scale": 1.0},
+            "norm": {"eps": 1e-6}, "layers": layers}
+
+
 def llama_like(z):
     return {"architectures": ["LlamaForCausalLM"], "num_hidden_layers": z["layers"], "hidden_size": z["width"],
             "num_attention_heads": z["heads"], "num_key_value_heads": z["kv_heads"], "head_dim": z["dim"],
@@ -486,26 +507,41 @@ def make_engine_any(cfg, max_tokens, max_batch):
     return engine
 
 
+DESIGNS = {
+    # name -> (configuration of a size, what the line's "model" says, the arms it runs beside)
+    "guduzen": (guduzen_config, "Guduzen, layers window attention / shared-cache attention / latent attention / delta rule",
+                ("llama",)),
+    "pekerax": (pekerax_config, "Pekerax, layers delta rule / attention / attention, first feed-forward dense, the others "
+                                "routed (8 experts, 2 per token)", ("guduzen", "llama")),
+}
+
+
 def run_design(args, peaks, peak_source, clocks) -> int:
-    """One line: per size, the Guduzen decoder and the Llama 3 decoder of equal width, depth, heads and vocabulary:
-    prompt and decode throughput and the device time of every kernel function in one prompt pass and one decode step."""
+    """One line: per size, the design's decoder and the decoders it is compared with, of equal width, depth, heads and
+    vocabulary: prompt and decode throughput and the device time of every kernel function in one prompt pass and one
+    decode step."""
     t0 = time.time()
     sizes = {}
+    name = args.design
+    make, what, beside = DESIGNS[name]
+    others = {"guduzen": guduzen_config, "llama": llama_like}
     for key in (args.design_sizes.split(",") if args.design_sizes else sorted(DESIGN_SIZES, reverse=True)):
         z = DESIGN_SIZES[key]
-        sizes[key] = {"sizes": z, "guduzen": run_design_arm(guduzen_config(z), f"guduzen {key}", args, peaks),
-                      "llama": run_design_arm(llama_like(z), f"llama {key}", args, peaks)}
+        sizes[key] = {"sizes": z, name: run_design_arm(make(z), f"{name} {key}", args, peaks)}
+        for other in beside:
+            sizes[key][other] = run_design_arm(others[other](z), f"{other} {key}", args, peaks)
     clock_summary = clocks.summary(t0, time.time())
     clocks.stop()
     first = sizes[next(iter(sizes))]
-    line = {"metric": "decode tokens/s (Guduzen decoder beside a Llama 3 decoder of equal size)",
-            "value": first["guduzen"]["decode_tokens_per_s"], "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": first["guduzen"]["decode_ms_per_step"], "higher_is_better": True,
+    line = {"metric": f"decode tokens/s ({name.capitalize()} decoder beside " + " and ".join(
+                f"a {'Llama 3' if o == 'llama' else o.capitalize()} decoder" for o in beside) + " of equal size)",
+            "value": first[name]["decode_tokens_per_s"], "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": first[name]["decode_ms_per_step"], "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic: random weights, uniform random token ids",
-            "config": {"model": "Guduzen, layers window attention / shared-cache attention / latent attention / delta rule",
+            "config": {"model": what,
                        "global_batch": args.batch, "seq_len": min(args.context, 2048), "parallelism": "single GPU"},
-            "peaks": {**peaks, "source": peak_source}, "sizes": sizes, "gpu_launches": first["guduzen"]["decode_launches"],
+            "peaks": {**peaks, "source": peak_source}, "sizes": sizes, "gpu_launches": first[name]["decode_launches"],
             "clocks": clock_summary, "impl": "ours"}
     print(json.dumps(line))
     return 0
@@ -528,8 +564,8 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-prefill", action="store_true", help="--model 3b/8b: skip the timed prompt step (launch lists of decode steps)")
-    ap.add_argument("--design", default=None, choices=["guduzen"],
-                    help="instead of the default workload: this decoder beside a Llama 3 decoder of equal size")
+    ap.add_argument("--design", default=None, choices=sorted(DESIGNS),
+                    help="instead of the default workload: this decoder beside the closest existing decoders of equal size")
     ap.add_argument("--design-sizes", default="", help="with --design: which of its sizes (s, m), with commas; default all")
     args = ap.parse_args()
 

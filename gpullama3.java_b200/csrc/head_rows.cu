@@ -13,7 +13,8 @@
 // rows ([page][kv_head][position][d_pad]) or as value rows (transposed, [page][kv_head][d_pad][position]), so that
 // a mixer without rotation needs no other kernel between its projection and attention.
 // Up to four such segments of a token's row are handled by one launch (queries, keys and values of an attention
-// layer; a latent that is stored once as keys and once as values).  A warp per (token, row).
+// layer; a latent that is stored once as keys and once as values).  A warp per (token, row), or a CTA per token when a
+// segment's norm runs over all its rows.
 #include "common.cuh"
 
 namespace b200 {
@@ -50,33 +51,18 @@ struct RowSegments {
     int total_rows;
 };
 
+// One (token, row): `whole` is the segment's 1 / rms when its norm runs over all its rows (made once per token by the
+// caller), unused otherwise.
 template <typename T>
-__global__ void __launch_bounds__(kRowThreads)
-head_rows_kernel(const T* __restrict__ src, int ld_src, T* __restrict__ dst, int ld_dst, const float* __restrict__ bias,
-                 const float* __restrict__ weight, RowSegments segs, float eps, CacheTarget cache, MixSource mix) {
-    const int t = blockIdx.x, lane = threadIdx.x & 31;
-    int row = blockIdx.y * (kRowThreads / 32) + (threadIdx.x >> 5);
-    if (row >= segs.total_rows) return;
-    int s = 0;
-    while (s + 1 < segs.n && row >= segs.seg[s].n_rows) {
-        row -= segs.seg[s].n_rows;
-        ++s;
-    }
-    const RowSegment g = segs.seg[s];
+__device__ __forceinline__ void head_row(const T* __restrict__ src, int ld_src, T* __restrict__ dst, int ld_dst,
+                                         const float* __restrict__ bias, const float* __restrict__ weight, const RowSegment& g,
+                                         int t, int row, int lane, float eps, float whole, const CacheTarget& cache,
+                                         const MixSource& mix) {
     const T* x = src + (size_t)t * ld_src + g.src_off + (size_t)row * g.d;
     const float* b = g.bias_off >= 0 ? bias + g.bias_off + (size_t)row * g.d : nullptr;
     float factor = g.mul;
-    if (g.norm == 2) {   // every warp of the segment sums the whole segment, in the same order
-        const T* xs = src + (size_t)t * ld_src + g.src_off;
-        const float* bs = g.bias_off >= 0 ? bias + g.bias_off : nullptr;
-        const int n = g.n_rows * g.d;
-        float ss = 0.f;
-        for (int e = lane; e < n; e += 32) {
-            const float z = to_f32<T>(xs[e]) + (bs ? bs[e] : 0.f);
-            ss += z * z;
-        }
-        ss = warp_sum(ss);
-        factor *= 1.0f / sqrtf(ss / (float)n + eps);
+    if (g.norm == 2) {
+        factor *= whole;
     } else if (g.norm) {
         float ss = 0.f;
         for (int e = lane; e < g.d; e += 32) {
@@ -110,6 +96,55 @@ head_rows_kernel(const T* __restrict__ src, int ld_src, T* __restrict__ dst, int
             if (other) z = (1.0f - lambda) * z + lambda * to_f32<T>(other[e]);
         }
         o[(size_t)e * step] = from_f32<T>(z);
+    }
+}
+
+// A warp per (token, row); grid (tokens, rows / warps).
+template <typename T>
+__global__ void __launch_bounds__(kRowThreads)
+head_rows_kernel(const T* __restrict__ src, int ld_src, T* __restrict__ dst, int ld_dst, const float* __restrict__ bias,
+                 const float* __restrict__ weight, RowSegments segs, float eps, CacheTarget cache, MixSource mix) {
+    const int t = blockIdx.x, lane = threadIdx.x & 31;
+    int row = blockIdx.y * (kRowThreads / 32) + (threadIdx.x >> 5);
+    if (row >= segs.total_rows) return;
+    int s = 0;
+    while (s + 1 < segs.n && row >= segs.seg[s].n_rows) {
+        row -= segs.seg[s].n_rows;
+        ++s;
+    }
+    head_row<T>(src, ld_src, dst, ld_dst, bias, weight, segs.seg[s], t, row, lane, eps, 0.f, cache, mix);
+}
+
+// A CTA per token, for launches in which some segment's norm runs over all its rows: the CTA sums such a segment once
+// (its threads in a fixed order), then its warps take the token's rows in turn.
+constexpr int kTokenThreads = 256;
+
+template <typename T>
+__global__ void __launch_bounds__(kTokenThreads)
+head_rows_token_kernel(const T* __restrict__ src, int ld_src, T* __restrict__ dst, int ld_dst, const float* __restrict__ bias,
+                       const float* __restrict__ weight, RowSegments segs, float eps, CacheTarget cache, MixSource mix) {
+    __shared__ float scratch[33];
+    __shared__ float whole[kRowSegments];
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int s = 0; s < segs.n; ++s) {
+        const RowSegment& g = segs.seg[s];
+        if (g.norm != 2) continue;
+        const T* xs = src + (size_t)t * ld_src + g.src_off;
+        const float* bs = g.bias_off >= 0 ? bias + g.bias_off : nullptr;
+        const int n = g.n_rows * g.d;
+        float ss = 0.f;
+        for (int e = threadIdx.x; e < n; e += kTokenThreads) {
+            const float z = to_f32<T>(xs[e]) + (bs ? bs[e] : 0.f);
+            ss += z * z;
+        }
+        ss = block_sum(ss, scratch);
+        if (threadIdx.x == 0) whole[s] = 1.0f / sqrtf(ss / (float)n + eps);
+    }
+    __syncthreads();
+    for (int s = 0; s < segs.n; ++s) {
+        const RowSegment& g = segs.seg[s];
+        for (int row = warp; row < g.n_rows; row += kTokenThreads / 32)
+            head_row<T>(src, ld_src, dst, ld_dst, bias, weight, g, t, row, lane, eps, whole[s], cache, mix);
     }
 }
 
@@ -153,6 +188,14 @@ extern "C" int b200_head_rows(const void* src, int ld_src, void* dst, int ld_dst
     if (grid.y > 65535) return b200::kErrUnsupportedSize;
     const b200::CacheTarget cache = {positions, seq_ids, page_table, table_stride, k_pool, v_pool};
     const b200::MixSource mix = {other, ld_other, lambda};
+    bool per_token = false;
+    for (int i = 0; i < n_segments; ++i) per_token = per_token || segs.seg[i].norm == 2;
+    if (per_token) {
+        B200_DISPATCH_DTYPE(dtype, T,
+            b200::head_rows_token_kernel<T><<<n_tokens, b200::kTokenThreads, 0, stream>>>((const T*)src, ld_src, (T*)dst, ld_dst,
+                                                                                          bias, weight, segs, eps, cache, mix));
+        return b200::launch_status();
+    }
     B200_DISPATCH_DTYPE(dtype, T,
         b200::head_rows_kernel<T><<<grid, b200::kRowThreads, 0, stream>>>((const T*)src, ld_src, (T*)dst, ld_dst, bias,
                                                                           weight, segs, eps, cache, mix));

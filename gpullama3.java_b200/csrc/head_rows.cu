@@ -115,8 +115,8 @@ head_rows_kernel(const T* __restrict__ src, int ld_src, T* __restrict__ dst, int
     head_row<T>(src, ld_src, dst, ld_dst, bias, weight, segs.seg[s], t, row, lane, eps, 0.f, cache, mix);
 }
 
-// A CTA per token, for launches in which some segment's norm runs over all its rows: the CTA sums such a segment once
-// (its threads in a fixed order), then its warps take the token's rows in turn.
+// For launches in which some segment's norm runs over all its rows: a CTA sums such a segment once (its threads in a
+// fixed order), then its warps take the token's rows in turn.
 constexpr int kTokenThreads = 256;
 
 template <typename T>
@@ -141,10 +141,16 @@ head_rows_token_kernel(const T* __restrict__ src, int ld_src, T* __restrict__ ds
         if (threadIdx.x == 0) whole[s] = 1.0f / sqrtf(ss / (float)n + eps);
     }
     __syncthreads();
-    for (int s = 0; s < segs.n; ++s) {
-        const RowSegment& g = segs.seg[s];
-        for (int row = warp; row < g.n_rows; row += kTokenThreads / 32)
-            head_row<T>(src, ld_src, dst, ld_dst, bias, weight, g, t, row, lane, eps, whole[s], cache, mix);
+    // the token's rows, numbered through the segments, are shared out among the warps of the token's CTAs (gridDim.y of
+    // them: a step of few tokens has several per token, each of which has summed for itself)
+    const int n_warps = (int)gridDim.y * (kTokenThreads / 32);
+    for (int flat = (int)blockIdx.y * (kTokenThreads / 32) + warp; flat < segs.total_rows; flat += n_warps) {
+        int s = 0, row = flat;
+        while (s + 1 < segs.n && row >= segs.seg[s].n_rows) {
+            row -= segs.seg[s].n_rows;
+            ++s;
+        }
+        head_row<T>(src, ld_src, dst, ld_dst, bias, weight, segs.seg[s], t, row, lane, eps, whole[s], cache, mix);
     }
 }
 
@@ -191,8 +197,11 @@ extern "C" int b200_head_rows(const void* src, int ld_src, void* dst, int ld_dst
     bool per_token = false;
     for (int i = 0; i < n_segments; ++i) per_token = per_token || segs.seg[i].norm == 2;
     if (per_token) {
+        const int per_cta_rows = b200::kTokenThreads / 32;
+        const int ny = n_tokens >= 512 ? 1 : (segs.total_rows + per_cta_rows - 1) / per_cta_rows;
+        const dim3 token_grid(n_tokens, ny > 16 ? 16 : ny);
         B200_DISPATCH_DTYPE(dtype, T,
-            b200::head_rows_token_kernel<T><<<n_tokens, b200::kTokenThreads, 0, stream>>>((const T*)src, ld_src, (T*)dst, ld_dst,
+            b200::head_rows_token_kernel<T><<<token_grid, b200::kTokenThreads, 0, stream>>>((const T*)src, ld_src, (T*)dst, ld_dst,
                                                                                           bias, weight, segs, eps, cache, mix));
         return b200::launch_status();
     }

@@ -4,18 +4,17 @@
 //                 The experts form `n_groups` equal groups of neighbours; a group's score is its best expert's score, and
 //                 only experts of the `keep_groups` best groups may be chosen.  The `top` allowed experts with the
 //                 largest scores are chosen (ties: the lower index); their weights are their scores over the sum of
-//                 the chosen scores (+ norm_eps).  A warp per token.
-//   moe_expert_up / moe_expert_down
-//                 the experts of every (token, chosen expert) pair as two weight-streaming kernels: a pair's gate and up
-//                 rows meet the token's input, the gated epilogue follows (the same codes as the products' gated
-//                 epilogues), and the down rows of a token's chosen experts meet its pairs' results, weighted and summed
-//                 in the order of choice into the 32-bit residual stream.  Which expert a pair uses is read on the device,
-//                 so a decode step's launches do not depend on the routing.
-//   moe_group / moe_gather / moe_combine
-//                 for prompts: the pairs are ordered by expert (counting sort; the order inside an expert's run does not
-//                 change any result, a row of a product depends on its own input row only), the inputs gathered into that
-//                 order, so that each expert's rows are one dense product for the tensor-core kernels, and the results
-//                 carried back, weighted, into the residual stream.
+//                 the chosen scores (+ norm_eps).  A CTA per token.
+//   moe_group     the (token, choice) pairs ordered by expert (counting sort; the order inside an expert's run does not
+//                 change any result, a row of a product depends on its own input row only).
+//   moe_rows      steps of few tokens: every expert's rows as a weight-streaming product whose row counts are read on
+//                 the device, so a decode step's launches do not depend on the routing; an expert's weights are read once
+//                 for all tokens that chose it (in groups of eight), an expert nobody chose is not read.  Used twice:
+//                 gate and up rows with the gated epilogue (the same codes as the products' gated epilogues), then down.
+//   moe_gather    prompts: the inputs copied into the order of their experts, so that each expert's rows are one dense
+//                 product for the tensor-core kernels.
+//   moe_combine   the experts' results carried back, weighted and summed in the order of choice, into the 32-bit
+//                 residual stream.
 #include "common.cuh"
 
 namespace b200 {
@@ -75,28 +74,33 @@ struct RouteArgs {
     float norm_eps;
 };
 
-constexpr int kRouteWarps = 4;
+constexpr int kRouteThreads = 128;
 
+// A CTA per token: its warps share out the experts' logits (16 bytes of a router row per lane and step when the rows
+// allow), then the first warp does the softmax and the choice.
 template <typename T>
-__global__ void __launch_bounds__(kRouteWarps * 32)
+__global__ void __launch_bounds__(kRouteThreads)
 moe_route_kernel(RouteArgs a) {
     extern __shared__ float smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    float* x = smem + (size_t)warp * (a.width + a.n_experts + a.n_groups);   // the token's input
-    float* s = x + a.width;                                                   // scores; chosen or barred ones turn negative
-    float* gs = s + a.n_experts;                                              // group scores
-    const int t = blockIdx.x * kRouteWarps + warp;
-    if (t >= a.n_tokens) return;
+    float* x = smem;                       // the token's input
+    float* s = x + a.width;                // logits, then scores; chosen or barred ones turn negative
+    float* gs = s + a.n_experts;           // group scores
+    const int t = blockIdx.x;
     const T* hr = (const T*)a.h + (size_t)t * a.ld_h;
-    for (int k = lane; k < a.width; k += 32) x[k] = to_f32<T>(hr[k]);
-    __syncwarp();
-    float m = -INFINITY;
-    for (int e = 0; e < a.n_experts; ++e) {
-        const float z = warp_dot<float, false>(a.router + (size_t)e * a.width, x, a.width, lane);
+    for (int k = threadIdx.x; k < a.width; k += kRouteThreads) x[k] = to_f32<T>(hr[k]);
+    __syncthreads();
+    const bool vec = a.width % 4 == 0 && ((uintptr_t)a.router & 15) == 0;
+    for (int e = warp; e < a.n_experts; e += kRouteThreads / 32) {
+        const float* w = a.router + (size_t)e * a.width;
+        const float z = vec ? warp_dot<float, true>(w, x, a.width, lane) : warp_dot<float, false>(w, x, a.width, lane);
         if (lane == 0) s[e] = z;
-        m = fmaxf(m, z);
     }
-    __syncwarp();
+    __syncthreads();
+    if (warp != 0) return;
+    float m = -INFINITY;
+    for (int e = lane; e < a.n_experts; e += 32) m = fmaxf(m, s[e]);
+    m = warp_max(m);
     float sum = 0.f;
     for (int e = lane; e < a.n_experts; e += 32) sum += expf(s[e] - m);
     sum = warp_sum(sum);
@@ -129,7 +133,7 @@ moe_route_kernel(RouteArgs a) {
             __syncwarp();
         }
         for (int e = lane; e < a.n_experts; e += 32)
-            if (gs[e / per] != -3.f) s[e] = -1.f - s[e];   // barred: negative, the score recoverable (never needed)
+            if (gs[e / per] != -3.f) s[e] = -1.f - s[e];   // barred: negative
         __syncwarp();
     }
     // the `top` best allowed experts, one after the other
@@ -158,7 +162,7 @@ moe_route_kernel(RouteArgs a) {
     }
 }
 
-// ------------------------------------------------------------------------------------------------ experts, pair by pair
+// ------------------------------------------------------------------------------------------------ experts, few rows each
 __device__ __forceinline__ float gated_value(float gate, float up, int act, float limit, float slope) {
     if (act == 2) {
         const float g = fminf(gate, limit), u = fminf(fmaxf(up, -limit), limit);
@@ -168,58 +172,145 @@ __device__ __forceinline__ float gated_value(float gate, float up, int act, floa
     return gate / (1.0f + expf(-gate)) * up;
 }
 
-constexpr int kExpertWarps = 4;
-constexpr int kUpPerWarp = 2;     // gate/up pairs a warp computes one after the other
+constexpr int kRowsWarps = 8;
+constexpr int kRowsTokens = 8;    // rows of A that meet a weight row while it is in registers
 
-// y[pair][j] = act(W_gu[e][2 j] . h[t], W_gu[e][2 j + 1] . h[t]);  grid (ceil(ff / (warps * kUpPerWarp)), pairs)
-template <typename T, bool VEC>
-__global__ void __launch_bounds__(kExpertWarps * 32)
-moe_expert_up_kernel(const T* __restrict__ h, int ld_h, const T* __restrict__ w_gu, const int* __restrict__ chosen,
-                     T* __restrict__ y, int width, int ff, int top, int act, float limit, float slope) {
-    extern __shared__ float x[];
-    const int pair = blockIdx.y, t = pair / top, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const T* hr = h + (size_t)t * ld_h;
-    for (int k = threadIdx.x; k < width; k += blockDim.x) x[k] = to_f32<T>(hr[k]);
-    __syncthreads();
-    const int e = chosen[pair];
-    const T* w = w_gu + (size_t)e * 2 * ff * width;
+struct RowsArgs {
+    const void* a;          // rows of A, [.][ld_a]: row order[p] / top when `order` is given, row p otherwise
+    int ld_a;
+    const int* order;
+    int top;
+    const void* w;          // [n_experts][n_out (2 n_out when gated: gate and up rows interleaved)][K]
+    const int* offsets;     // [n_experts + 1]: expert e owns places offsets[e] .. offsets[e + 1] - 1
+    void* out;              // gated: [.][ld_out] of the run's type; plain: 32-bit
+    int ld_out;
+    int K, n_out, units_per_cta;
+    int act;
+    float limit, slope;
+};
+
+__device__ __forceinline__ uint4 load_streamed(const void* p) {    // weights pass once: they need not stay in L1
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+template <typename T> __device__ __forceinline__ void unpack16(const uint4& v, float* f);
+template <> __device__ __forceinline__ void unpack16<float>(const uint4& v, float* f) {
+    f[0] = __uint_as_float(v.x); f[1] = __uint_as_float(v.y); f[2] = __uint_as_float(v.z); f[3] = __uint_as_float(v.w);
+}
+template <> __device__ __forceinline__ void unpack16<__nv_bfloat16>(const uint4& v, float* f) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-    for (int i = 0; i < kUpPerWarp; ++i) {
-        const int j = (blockIdx.x * kExpertWarps + warp) * kUpPerWarp + i;
-        if (j >= ff) break;
-        const float gate = warp_dot<T, VEC>(w + (size_t)(2 * j) * width, x, width, lane);
-        const float up = warp_dot<T, VEC>(w + (size_t)(2 * j + 1) * width, x, width, lane);
-        if (lane == 0) y[(size_t)pair * ff + j] = from_f32<T>(gated_value(gate, up, act, limit, slope));
+    for (int i = 0; i < 4; ++i) {
+        f[2 * i] = __uint_as_float(w[i] << 16);
+        f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
     }
 }
 
-constexpr int kDownPerWarp = 2;
-
-// residual[t][c] += sum_k weights[t][k] (W_down[e_k][c] . y[t top + k]);  grid (ceil(width / (warps * kDownPerWarp)), T)
-template <typename T, bool VEC>
-__global__ void __launch_bounds__(kExpertWarps * 32)
-moe_expert_down_kernel(const T* __restrict__ y, const T* __restrict__ w_down, const int* __restrict__ chosen,
-                       const float* __restrict__ weights, float* __restrict__ residual, int width, int ff, int top) {
-    extern __shared__ float ys[];          // [top][ff]
-    __shared__ int e_s[kMaxTop];
-    __shared__ float w_s[kMaxTop];
-    const int t = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int i = threadIdx.x; i < top * ff; i += blockDim.x) ys[i] = to_f32<T>(y[(size_t)t * top * ff + i]);
-    if (threadIdx.x < top) {
-        e_s[threadIdx.x] = chosen[(size_t)t * top + threadIdx.x];
-        w_s[threadIdx.x] = weights[(size_t)t * top + threadIdx.x];
-    }
-    __syncthreads();
-#pragma unroll
-    for (int i = 0; i < kDownPerWarp; ++i) {
-        const int c = (blockIdx.x * kExpertWarps + warp) * kDownPerWarp + i;
-        if (c >= width) break;
-        float total = 0.f;
-        for (int k = 0; k < top; ++k) {
-            const T* w = w_down + ((size_t)e_s[k] * width + c) * ff;
-            total += w_s[k] * warp_dot<T, VEC>(w, ys + (size_t)k * ff, ff, lane);
+// out[p] = A[row(p)] W_e^T (gated: act of the gate and up sums) for the places p of expert e = blockIdx.y: a weight-
+// streaming product.  The CTA stages up to kRowsTokens rows of A in shared memory; a warp carries two weight rows at a
+// time through its registers (a gate row and its up row, or two neighbouring rows of a plain product), four 16-byte
+// pieces of each in flight, once per staged group, and keeps a sum per staged row and weight row.  An expert nobody
+// chose costs its CTAs one read of two integers.  Sums run over k in a fixed order: a row's result does not depend on
+// its place.
+template <typename T, bool GATED, bool VEC>
+__global__ void __launch_bounds__(kRowsWarps * 32)
+moe_rows_kernel(RowsArgs r) {
+    extern __shared__ __align__(16) unsigned char raw[];
+    T* xs = reinterpret_cast<T*>(raw);                 // [kRowsTokens][K]
+    constexpr int E = Piece<T>::kElems;
+    const int e = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int lo = r.offsets[e], hi = r.offsets[e + 1];
+    if (hi <= lo) return;
+    const int n_rows = GATED ? 2 * r.n_out : r.n_out;  // weight rows of the expert
+    const T* w = (const T*)r.w + (size_t)e * n_rows * r.K;
+    for (int g0 = lo; g0 < hi; g0 += kRowsTokens) {
+        const int cnt = min(kRowsTokens, hi - g0);
+        __syncthreads();                               // (the group before has been read)
+        for (int m = 0; m < cnt; ++m) {
+            const int p = g0 + m;
+            const T* src = (const T*)r.a + (size_t)(r.order ? r.order[p] / r.top : p) * r.ld_a;
+            if (VEC) {
+                for (int k = threadIdx.x * E; k < r.K; k += kRowsWarps * 32 * E)
+                    *reinterpret_cast<uint4*>(xs + (size_t)m * r.K + k) = *reinterpret_cast<const uint4*>(src + k);
+            } else {
+                for (int k = threadIdx.x; k < r.K; k += kRowsWarps * 32) xs[(size_t)m * r.K + k] = src[k];
+            }
         }
-        if (lane == 0) residual[(size_t)t * width + c] += total;
+        __syncthreads();
+        for (int unit = warp; unit < r.units_per_cta; unit += kRowsWarps) {
+            const int row0 = 2 * (blockIdx.x * r.units_per_cta + unit);      // this warp's two weight rows: row0, row0 + 1
+            if (row0 >= n_rows) break;
+            const bool second = row0 + 1 < n_rows;
+            const T* w0 = w + (size_t)row0 * r.K;
+            const T* w1 = second ? w0 + r.K : w0;
+            float acc0[kRowsTokens], acc1[kRowsTokens];
+#pragma unroll
+            for (int m = 0; m < kRowsTokens; ++m) acc0[m] = acc1[m] = 0.f;
+            if (VEC) {
+                constexpr int U = 4;                   // pieces of each row in flight
+                for (int k0 = lane * E; k0 < r.K; k0 += U * 32 * E) {
+                    uint4 p0[U], p1[U];
+#pragma unroll
+                    for (int u = 0; u < U; ++u) {
+                        const int k = k0 + u * 32 * E;
+                        if (k < r.K) {
+                            p0[u] = load_streamed(w0 + k);
+                            p1[u] = load_streamed(w1 + k);
+                        }
+                    }
+#pragma unroll
+                    for (int u = 0; u < U; ++u) {
+                        const int k = k0 + u * 32 * E;
+                        if (k < r.K) {
+                            float f0[E], f1[E];
+                            unpack16<T>(p0[u], f0);
+                            unpack16<T>(p1[u], f1);
+#pragma unroll
+                            for (int m = 0; m < kRowsTokens; ++m) {
+                                if (m < cnt) {
+                                    float xv[E];
+                                    Piece<T>::load(xs + (size_t)m * r.K + k, xv);
+#pragma unroll
+                                    for (int i = 0; i < E; ++i) {
+                                        acc0[m] += f0[i] * xv[i];
+                                        acc1[m] += f1[i] * xv[i];
+                                    }
+                                }
+                            }
+                        }
+                    }
+                }
+            } else {
+                for (int k = lane; k < r.K; k += 32) {
+                    const float a0 = to_f32<T>(w0[k]), a1 = to_f32<T>(w1[k]);
+#pragma unroll
+                    for (int m = 0; m < kRowsTokens; ++m) {
+                        if (m < cnt) {
+                            const float xv = to_f32<T>(xs[(size_t)m * r.K + k]);
+                            acc0[m] += a0 * xv;
+                            acc1[m] += a1 * xv;
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int m = 0; m < kRowsTokens; ++m) {
+                if (m < cnt) {
+                    const float s0 = warp_sum(acc0[m]), s1 = warp_sum(acc1[m]);
+                    if (lane == 0) {
+                        const size_t at = (size_t)(g0 + m) * r.ld_out;
+                        if (GATED) {
+                            ((T*)r.out)[at + row0 / 2] = from_f32<T>(gated_value(s0, s1, r.act, r.limit, r.slope));
+                        } else {
+                            ((float*)r.out)[at + row0] = s0;
+                            if (second) ((float*)r.out)[at + row0 + 1] = s1;
+                        }
+                    }
+                }
+            }
+        }
     }
 }
 
@@ -283,7 +374,7 @@ extern "C" int b200_moe_route(const void* h, int ld_h, int dtype, const float* r
     if (n_experts < 1 || n_experts > b200::kMaxExperts || top < 1 || top > 32 || top > n_experts || n_groups < 1 ||
         n_experts % n_groups || keep_groups < 1 || keep_groups > n_groups || top > keep_groups * (n_experts / n_groups))
         return b200::kErrBadArgument;
-    const size_t smem = sizeof(float) * b200::kRouteWarps * ((size_t)width + n_experts + n_groups);
+    const size_t smem = sizeof(float) * ((size_t)width + n_experts + n_groups);
     if (smem > 200 * 1024) return b200::kErrUnsupportedSize;
     const b200::RouteArgs a = {h, ld_h, router, chosen, weights, scores, n_tokens, width, n_experts, n_groups, keep_groups, top, norm_eps};
     B200_DISPATCH_DTYPE(dtype, T,
@@ -292,39 +383,38 @@ extern "C" int b200_moe_route(const void* h, int ld_h, int dtype, const float* r
             const int e = (int)cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (e != 0) return e;
         }
-        kernel<<<(n_tokens + b200::kRouteWarps - 1) / b200::kRouteWarps, b200::kRouteWarps * 32, smem, stream>>>(a));
+        kernel<<<n_tokens, b200::kRouteThreads, smem, stream>>>(a));
     return b200::launch_status();
 }
 
-// h [T][ld_h]; w_gu [n_experts][2 ff][width] (gate and up rows interleaved); w_down [n_experts][width][ff];
-// y [T top][ff] scratch of the run's type; residual [T][width] 32-bit.  act: 0 SiLU, 1 GELU (tanh form), 2 clamped.
-extern "C" int b200_moe_experts(const void* h, int ld_h, int dtype, const void* w_gu, const void* w_down, const int* chosen,
-                                const float* weights, void* y, float* residual, int n_tokens, int width, int ff, int top,
-                                int act, float limit, float slope, cudaStream_t stream) {
-    if (n_tokens <= 0) return 0;
-    if (top < 1 || top > b200::kMaxTop || width < 1 || ff < 1 || act < 0 || act > 2) return b200::kErrBadArgument;
-    const long long pairs = (long long)n_tokens * top;
-    if (pairs > 65535 || n_tokens > 65535) return b200::kErrUnsupportedSize;
-    const size_t smem_up = sizeof(float) * width, smem_down = sizeof(float) * (size_t)top * ff;
-    if (smem_up > 200 * 1024 || smem_down > 200 * 1024) return b200::kErrUnsupportedSize;
-    const int el = dtype == b200::kF32 ? 4 : 8;
-    const bool vec = width % el == 0 && ff % el == 0 && ld_h % el == 0 &&
-                     ((((uintptr_t)w_gu) | ((uintptr_t)w_down)) & 15) == 0;
-    const dim3 grid_up((ff + b200::kExpertWarps * b200::kUpPerWarp - 1) / (b200::kExpertWarps * b200::kUpPerWarp), (unsigned)pairs);
-    const dim3 grid_down((width + b200::kExpertWarps * b200::kDownPerWarp - 1) / (b200::kExpertWarps * b200::kDownPerWarp), n_tokens);
-#define B200_MOE_GO(T, VEC)                                                                                                  \
-    do {                                                                                                                     \
-        auto up = b200::moe_expert_up_kernel<T, VEC>;                                                                        \
-        auto down = b200::moe_expert_down_kernel<T, VEC>;                                                                    \
-        if (smem_up > 48 * 1024) cudaFuncSetAttribute(up, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_up);        \
-        if (smem_down > 48 * 1024) cudaFuncSetAttribute(down, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_down);  \
-        up<<<grid_up, b200::kExpertWarps * 32, smem_up, stream>>>((const T*)h, ld_h, (const T*)w_gu, chosen, (T*)y, width, ff, \
-                                                                  top, act, limit, slope);                                   \
-        down<<<grid_down, b200::kExpertWarps * 32, smem_down, stream>>>((const T*)y, (const T*)w_down, chosen, weights,      \
-                                                                        residual, width, ff, top);                           \
+// One product per expert over the places offsets[e] .. offsets[e + 1] - 1 (see moe_rows_kernel).  gated: w holds gate
+// and up rows interleaved and `out` is of the run's type; else `out` is 32-bit.  act: 0 SiLU, 1 GELU (tanh form), 2 clamped.
+extern "C" int b200_moe_rows(const void* a, int ld_a, int dtype, const int* order, int top, const void* w, const int* offsets,
+                             void* out, int ld_out, int n_experts, int K, int n_out, int gated, int act, float limit,
+                             float slope, cudaStream_t stream) {
+    if (n_experts <= 0 || n_out <= 0) return 0;
+    if (K < 1 || act < 0 || act > 2 || (order && top < 1) || n_experts > 65535) return b200::kErrBadArgument;
+    const size_t el = dtype == b200::kF32 ? 4 : 2;
+    const size_t smem = (size_t)b200::kRowsTokens * K * el;
+    if (smem > 200 * 1024) return b200::kErrUnsupportedSize;
+    const int per16 = 16 / (int)el;
+    const bool vec = K % per16 == 0 && ld_a % per16 == 0 && ((((uintptr_t)a) | ((uintptr_t)w)) & 15) == 0;
+    const int units = gated ? n_out : (n_out + 1) / 2;     // pairs of weight rows
+    b200::RowsArgs r = {a, ld_a, order, top, w, offsets, out, ld_out, K, n_out, units >= 1024 ? 16 : 8, act, limit, slope};
+    const dim3 grid((units + r.units_per_cta - 1) / r.units_per_cta, n_experts);
+#define B200_ROWS_GO(T, G, V)                                                                                         \
+    do {                                                                                                              \
+        auto kernel = b200::moe_rows_kernel<T, G, V>;                                                                 \
+        if (smem > 48 * 1024) {                                                                                       \
+            const int e = (int)cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
+            if (e != 0) return e;                                                                                     \
+        }                                                                                                             \
+        kernel<<<grid, b200::kRowsWarps * 32, smem, stream>>>(r);                                                     \
     } while (0)
-    B200_DISPATCH_DTYPE(dtype, T, if (vec) B200_MOE_GO(T, true); else B200_MOE_GO(T, false));
-#undef B200_MOE_GO
+    B200_DISPATCH_DTYPE(dtype, T,
+        if (gated) { if (vec) B200_ROWS_GO(T, true, true); else B200_ROWS_GO(T, true, false); }
+        else { if (vec) B200_ROWS_GO(T, false, true); else B200_ROWS_GO(T, false, false); });
+#undef B200_ROWS_GO
     return b200::launch_status();
 }
 

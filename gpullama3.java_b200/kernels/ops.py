@@ -94,8 +94,8 @@ _SIGNATURES = {
                                             c_int, c_int, c_int, c_int, c_float, c_float, c_int]),
     "b200_moe_route": ("moe", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                c_int, c_int, c_float]),
-    "b200_moe_experts": ("moe", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
-                                 c_int, c_int, c_int, c_int, c_float, c_float]),
+    "b200_moe_rows": ("moe", [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                              c_int, c_int, c_int, c_float, c_float]),
     "b200_moe_group": ("moe", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "b200_moe_gather": ("moe", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int]),
     "b200_moe_combine": ("moe", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int]),
@@ -938,22 +938,23 @@ def moe_route(h: torch.Tensor, router: torch.Tensor, chosen: torch.Tensor, weigh
                                  int(n_groups), int(keep_groups), chosen.shape[1], float(norm_eps), _stream()), "moe_route")
 
 
-def moe_experts(h: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, chosen: torch.Tensor, weights: torch.Tensor,
-                y: torch.Tensor, residual: torch.Tensor, activation: str, gate_args=(0.0, 0.0)) -> None:
-    """residual[t] += sum_k weights[t, k] down_e( act(gate_e h[t], up_e h[t]) ), e = chosen[t, k]: every (token,
-    expert) pair as a weight-streaming product.  w_gate_up [E, 2 ff, width] (gate and up rows interleaved), w_down
-    [E, width, ff], y [T top, ff] scratch of h's dtype."""
-    _dev(h, w_gate_up, w_down, chosen, weights, y, residual)
-    T, width = h.shape
-    E, ff2, _ = w_gate_up.shape
-    top = chosen.shape[1]
-    assert h.dtype == w_gate_up.dtype == w_down.dtype == y.dtype and residual.dtype == torch.float32
-    assert w_gate_up.is_contiguous() and w_down.is_contiguous() and y.is_contiguous() and residual.is_contiguous()
-    assert tuple(w_down.shape) == (E, width, ff2 // 2) and tuple(y.shape) == (T * top, ff2 // 2) and h.stride(1) == 1
-    _check(_fn("b200_moe_experts")(h.data_ptr(), h.stride(0), dtype_code(h.dtype), w_gate_up.data_ptr(), w_down.data_ptr(),
-                                   chosen.data_ptr(), weights.data_ptr(), y.data_ptr(), residual.data_ptr(), T, width,
-                                   ff2 // 2, top, ACTIVATION_CODES[activation], float(gate_args[0]), float(gate_args[1]),
-                                   _stream()), "moe_experts")
+def moe_rows(a: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor, out: torch.Tensor, *, order: torch.Tensor | None = None,
+             top: int = 1, activation: str | None = None, gate_args=(0.0, 0.0)) -> None:
+    """One weight-streaming product per expert: out[p] = a[row(p)] @ w[e].T for the places p = offsets[e] ..
+    offsets[e + 1] - 1 of expert e, row(p) = order[p] // top when ``order`` is given, p otherwise.  With ``activation``
+    w [E, 2 n, K] holds gate and up rows interleaved and out [P, n] (a's dtype) receives the gated values; without, w
+    [E, n, K] and out [P, n] float32.  The row counts are read on the device."""
+    _dev(a, w, offsets, out, order)
+    E, rows, K = w.shape
+    gated = activation is not None
+    n_out = rows // 2 if gated else rows
+    assert a.dtype == w.dtype and w.is_contiguous() and a.stride(1) == 1 and a.shape[1] == K and out.stride(1) == 1
+    assert out.shape[1] == n_out and out.dtype == (a.dtype if gated else torch.float32)
+    assert offsets.dtype == torch.int32 and offsets.numel() == E + 1 and (order is None or order.dtype == torch.int32)
+    _check(_fn("b200_moe_rows")(a.data_ptr(), a.stride(0), dtype_code(a.dtype), order.data_ptr() if order is not None else None,
+                                int(top), w.data_ptr(), offsets.data_ptr(), out.data_ptr(), out.stride(0), E, K, n_out,
+                                1 if gated else 0, ACTIVATION_CODES[activation] if gated else 0, float(gate_args[0]),
+                                float(gate_args[1]), _stream()), "moe_rows")
 
 
 def moe_group(chosen: torch.Tensor, n_experts: int, offsets: torch.Tensor, order: torch.Tensor, place: torch.Tensor) -> None:

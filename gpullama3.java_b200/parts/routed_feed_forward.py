@@ -5,11 +5,12 @@
     ``keep_groups`` best groups can be chosen; the ``top`` best of those are
     y = sum over the chosen e of  s_e / (sum of the chosen s + 1e-20) * down_e( act(gate_e h, up_e h) )
 
-The router and the weights are 32-bit in both precisions.  A step of few tokens runs every (token, expert) pair as a
-weight-streaming product whose expert is read on the device, so a decode step's launches do not depend on the
-routing and can be recorded.  A prompt's pairs are ordered by expert, and every expert's rows are one product of the
-same kernels the dense feed-forward uses (gated epilogue included); the per-expert row counts come back to the host
-for that, which is why a prompt pass of this part is not replayed from a recording."""
+The router and the weights are 32-bit in both precisions.  The (token, choice) pairs are ordered by expert.  A step of
+few tokens then runs every expert's rows as a weight-streaming product whose row counts are read on the device, so a
+decode step's launches do not depend on the routing and can be recorded; an expert's weights are read once for all the
+tokens that chose it, and not at all when none did.  A prompt's rows are one product per expert of the same kernels the
+dense feed-forward uses (gated epilogue included); the per-expert row counts come back to the host for that, which is
+why a prompt pass of this part is not replayed from a recording."""
 from __future__ import annotations
 
 import torch
@@ -73,32 +74,33 @@ class RoutedFeedForward(FeedForward):
         ops.moe_route(x, self.router, chosen, weights, self.groups, self.keep_groups, self.weight_eps, scores)
         return chosen, weights
 
-    def by_expert(self, ctx: StepContext, n_tokens: int) -> bool:
-        """Whether the step's pairs are ordered by expert and run as one product per expert (prompts), or pair by pair."""
-        pairs = n_tokens * self.top
-        return not ctx.all_decode and n_tokens > 64 and pairs >= 8 * self.n_experts or pairs > 65535
+    def on_host(self, ctx: StepContext, n_tokens: int) -> bool:
+        """Whether the experts' products are launched from the host's knowledge of their row counts (prompts: dense
+        products on the tensor cores), or by kernels that read the counts on the device (steps of few tokens)."""
+        return (not ctx.all_decode) and n_tokens > 64 and n_tokens * self.top >= 16 * self.n_experts
 
     def forward(self, x, ctx: StepContext, residual, then_norm=None):
         T = x.shape[0]
         chosen, weights = self.route(x, ctx)
-        if not self.by_expert(ctx, T):
-            y = ctx.empty((T * self.top, self.intermediate_size), ctx.dtype)
-            ops.moe_experts(x, self.w_gate_up, self.w_down, chosen, weights, y, residual, self.activation, self.gate_args)
-            return None
         pairs = T * self.top
         offsets = ctx.empty((self.n_experts + 1,), torch.int32)
         order, place = ctx.empty((pairs,), torch.int32), ctx.empty((pairs,), torch.int32)
         ops.moe_group(chosen, self.n_experts, offsets, order, place)
-        bounds = offsets.tolist()                                   # (waits for the routing: the products' row counts)
-        xs = ctx.empty((pairs, self.hidden_size), ctx.dtype)
-        ops.moe_gather(x, order, xs, self.top)
         y = ctx.empty((pairs, self.intermediate_size), ctx.dtype)
         o = ctx.empty((pairs, self.hidden_size), torch.float32)
-        for e in range(self.n_experts):
-            lo, hi = bounds[e], bounds[e + 1]
-            if hi > lo:
-                self.gate_up[e].gated_into(xs[lo:hi], y[lo:hi], self.activation, self.gate_args)
-                self.down[e].into(y[lo:hi], o[lo:hi])
+        if not self.on_host(ctx, T):
+            ops.moe_rows(x, self.w_gate_up, offsets, y, order=order, top=self.top, activation=self.activation,
+                         gate_args=self.gate_args)
+            ops.moe_rows(y, self.w_down, offsets, o)
+        else:
+            bounds = offsets.tolist()                               # (waits for the routing: the products' row counts)
+            xs = ctx.empty((pairs, self.hidden_size), ctx.dtype)
+            ops.moe_gather(x, order, xs, self.top)
+            for e in range(self.n_experts):
+                lo, hi = bounds[e], bounds[e + 1]
+                if hi > lo:
+                    self.gate_up[e].gated_into(xs[lo:hi], y[lo:hi], self.activation, self.gate_args)
+                    self.down[e].into(y[lo:hi], o[lo:hi])
         ops.moe_combine(o, place, weights, residual)
         return None
 

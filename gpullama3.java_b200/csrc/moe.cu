@@ -11,6 +11,7 @@
 //                 the device, so a decode step's launches do not depend on the routing; an expert's weights are read once
 //                 for all tokens that chose it (in groups of eight), an expert nobody chose is not read.  Used twice:
 //                 gate and up rows with the gated epilogue (the same codes as the products' gated epilogues), then down.
+//                 bfloat16 runs on the tensor cores (mma.sync, the eight rows as a tile's columns), float32 on the FMA pipe.
 //   moe_gather    prompts: the inputs copied into the order of their experts, so that each expert's rows are one dense
 //                 product for the tensor-core kernels.
 //   moe_combine   the experts' results carried back, weighted and summed in the order of choice, into the 32-bit
@@ -314,6 +315,110 @@ moe_rows_kernel(RowsArgs r) {
     }
 }
 
+// The same product for bfloat16 on the tensor cores (mma.sync m16n8k16): the eight staged rows of A are the eight
+// columns of the tiles, sixteen weight rows their rows.  A lane loads 16 bytes of weight rows g and g + 8 (the 8 t-th
+// elements of a block of 32 along K) and 16 bytes of staged row g at the same place; the four pairs of those elements
+// feed two MMAs, which amounts to a fixed permutation of K inside the block, the same for both operands.  A CTA of
+// eight warps owns 8 / KS tiles of weight rows and cuts K into KS parts, one warp per (tile, part), up to eight blocks of
+// each weight row in flight per lane; the parts' sums meet in shared memory and are added in part order.  Rows of the
+// group that do not exist are zeros.
+__device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <bool GATED>
+__global__ void __launch_bounds__(kRowsWarps * 32)
+moe_rows_mma_kernel(RowsArgs r, int k_parts) {
+    extern __shared__ __align__(16) unsigned char raw[];
+    const int ldx = r.K + 8;                                    // (16 bytes of padding: the eight rows start in different banks)
+    __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(raw);  // [kRowsTokens][ldx]
+    float* part = reinterpret_cast<float*>(xs + (size_t)kRowsTokens * ldx);   // [kRowsWarps][32][4]
+    const int e = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int lo = r.offsets[e], hi = r.offsets[e + 1];
+    if (hi <= lo) return;
+    const int n_rows = GATED ? 2 * r.n_out : r.n_out;
+    const __nv_bfloat16* w = (const __nv_bfloat16*)r.w + (size_t)e * n_rows * r.K;
+    const int tiles_per_cta = kRowsWarps / k_parts, tile = warp / k_parts, kp = warp % k_parts;
+    const int row0 = (blockIdx.x * tiles_per_cta + tile) * 16;
+    const int n_kb = r.K / 32, per_part = (n_kb + k_parts - 1) / k_parts;
+    const int kb_lo = kp * per_part, kb_hi = min(n_kb, kb_lo + per_part);
+    const bool live = row0 < n_rows;
+    const __nv_bfloat16* wa = w + (size_t)min(row0 + g, n_rows - 1) * r.K + 8 * t;       // (rows beyond the last: read, never stored)
+    const __nv_bfloat16* wb = w + (size_t)min(row0 + g + 8, n_rows - 1) * r.K + 8 * t;
+    for (int g0 = lo; g0 < hi; g0 += kRowsTokens) {
+        const int cnt = min(kRowsTokens, hi - g0);
+        __syncthreads();                               // (the group before has been read, its partial sums too)
+        for (int m = 0; m < kRowsTokens; ++m) {
+            uint4* dst = reinterpret_cast<uint4*>(xs + (size_t)m * ldx);
+            if (m < cnt) {
+                const int p = g0 + m;
+                const uint4* src = reinterpret_cast<const uint4*>((const __nv_bfloat16*)r.a + (size_t)(r.order ? r.order[p] / r.top : p) * r.ld_a);
+                for (int i = threadIdx.x; i < r.K / 8; i += kRowsWarps * 32) dst[i] = src[i];
+            } else {
+                for (int i = threadIdx.x; i < r.K / 8; i += kRowsWarps * 32) dst[i] = make_uint4(0, 0, 0, 0);
+            }
+        }
+        __syncthreads();
+        float d[4] = {0.f, 0.f, 0.f, 0.f};
+        if (live) {
+            constexpr int U = 8;
+            const __nv_bfloat16* xr = xs + (size_t)g * ldx + 8 * t;
+            for (int kb = kb_lo; kb < kb_hi; kb += U) {
+                uint4 A[U], B[U];
+#pragma unroll
+                for (int u = 0; u < U; ++u)
+                    if (kb + u < kb_hi) {
+                        A[u] = load_streamed(wa + (size_t)(kb + u) * 32);
+                        B[u] = load_streamed(wb + (size_t)(kb + u) * 32);
+                    }
+#pragma unroll
+                for (int u = 0; u < U; ++u)
+                    if (kb + u < kb_hi) {
+                        const uint4 X = *reinterpret_cast<const uint4*>(xr + (size_t)(kb + u) * 32);
+                        mma_bf16(d, A[u].x, B[u].x, A[u].y, B[u].y, X.x, X.y);
+                        mma_bf16(d, A[u].z, B[u].z, A[u].w, B[u].w, X.z, X.w);
+                    }
+            }
+        }
+        if (k_parts > 1) {
+            float4* mine = reinterpret_cast<float4*>(part) + warp * 32 + lane;
+            *mine = make_float4(d[0], d[1], d[2], d[3]);
+            __syncthreads();
+            if (kp == 0) {
+                for (int q = 1; q < k_parts; ++q) {
+                    const float4 o = reinterpret_cast<const float4*>(part)[(warp + q) * 32 + lane];
+                    d[0] += o.x; d[1] += o.y; d[2] += o.z; d[3] += o.w;
+                }
+            }
+        }
+        if (live && kp == 0) {
+            // d[0], d[1]: weight row row0 + g, staged rows 2 t and 2 t + 1;  d[2], d[3]: weight row row0 + g + 8
+            if (GATED) {
+                float up[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) up[i] = __shfl_xor_sync(0xffffffffu, d[i], 4);   // the odd row next to this even one
+                if ((g & 1) == 0) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int m = 2 * t + (i & 1), row = row0 + g + (i >> 1) * 8;
+                        if (m < cnt && row + 1 < n_rows)
+                            ((__nv_bfloat16*)r.out)[(size_t)(g0 + m) * r.ld_out + row / 2] =
+                                __float2bfloat16_rn(gated_value(d[i], up[i], r.act, r.limit, r.slope));
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int m = 2 * t + (i & 1), row = row0 + g + (i >> 1) * 8;
+                    if (m < cnt && row < n_rows) ((float*)r.out)[(size_t)(g0 + m) * r.ld_out + row] = d[i];
+                }
+            }
+        }
+    }
+}
+
 // ------------------------------------------------------------------------------------------------ prompts: order by expert
 // One CTA.  offsets[e] .. offsets[e + 1]: the run of expert e among the ordered pairs; order[p]: which pair stands at
 // place p; place[pair]: where a pair stands.
@@ -402,6 +507,31 @@ extern "C" int b200_moe_rows(const void* a, int ld_a, int dtype, const int* orde
     const int units = gated ? n_out : (n_out + 1) / 2;     // pairs of weight rows
     b200::RowsArgs r = {a, ld_a, order, top, w, offsets, out, ld_out, K, n_out, units >= 1024 ? 16 : 8, act, limit, slope};
     const dim3 grid((units + r.units_per_cta - 1) / r.units_per_cta, n_experts);
+    if (dtype == b200::kBF16 && vec && K % 32 == 0) {
+        // tensor cores: tiles of 16 weight rows; K is cut among a CTA's warps until the grid has about eight CTAs per SM (the
+        // experts nobody chose leave theirs at once, and short CTAs even out what the SMs get)
+        const long long tiles = (long long)((gated ? 2 * n_out : n_out) + 15) / 16 * n_experts;
+        int k_parts = 1;
+        while (k_parts < b200::kRowsWarps && tiles * k_parts / b200::kRowsWarps < 8LL * b200::device_sm_count() && K / 32 >= 2 * k_parts)
+            k_parts *= 2;
+        const int per_cta = b200::kRowsWarps / k_parts;
+        const dim3 mma_grid(((gated ? 2 * n_out : n_out) + 16 * per_cta - 1) / (16 * per_cta), n_experts);
+        const size_t mma_smem = (size_t)b200::kRowsTokens * (K + 8) * 2 + sizeof(float) * b200::kRowsWarps * 32 * 4;
+        if (mma_smem <= 200 * 1024) {
+            if (gated) {
+                auto kernel = b200::moe_rows_mma_kernel<true>;
+                if (mma_smem > 48 * 1024 && cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)mma_smem) != cudaSuccess)
+                    return (int)cudaGetLastError();
+                kernel<<<mma_grid, b200::kRowsWarps * 32, mma_smem, stream>>>(r, k_parts);
+            } else {
+                auto kernel = b200::moe_rows_mma_kernel<false>;
+                if (mma_smem > 48 * 1024 && cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)mma_smem) != cudaSuccess)
+                    return (int)cudaGetLastError();
+                kernel<<<mma_grid, b200::kRowsWarps * 32, mma_smem, stream>>>(r, k_parts);
+            }
+            return b200::launch_status();
+        }
+    }
 #define B200_ROWS_GO(T, G, V)                                                                                         \
     do {                                                                                                              \
         auto kernel = b200::moe_rows_kernel<T, G, V>;                                                                 \

@@ -25,6 +25,7 @@
 // Three kernels share these roles and epilogues: the one just described; pairs of CTAs on 256-row tiles
 // (gemm_tcgen05_pair_kernel, tcgen05 cta_group::2), which large products take; and K cut into spans over a cluster
 // (gemm_tcgen05_spans_kernel) for few tiles with a long K.  Tiles are walked in bands of rows (tile_coords).
+// gemm_tcgen05_grouped_kernel: several products of one shape over runs of rows whose lengths are read on the device.
 // Edges: TMA zero-fills rows and K beyond the tensors, stores are bounds-checked, so any M, N and
 // any K that keeps rows 16-byte aligned (K % 8 == 0) are accepted.
 // Every mbarrier wait is bounded: when a wait gives up, the kernel records a code in a status
@@ -414,6 +415,151 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         }
         // the reductions this thread issued are complete (their sums are in C) before the kernel ends
         if (EPI == 1 && reduce_c && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    }
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(2 * BN) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Several products of one shape in one launch, each over its own run of rows (a routed feed-forward's experts):
+//     C[p, :] = A[p, :] W_g^T   for the rows p = offsets[g] .. offsets[g + 1] - 1 of group g,  W = [groups][N][K]
+// The runs' lengths are read on the device (they are a routing's outcome), so the host launches one grid for the most
+// tiles there can be and every CTA builds the same table: group g owns the tiles first[g] .. first[g + 1] - 1, down its
+// rows first.  A tile's loads may reach past its run's end into the next group's rows (or past the end of A, which
+// reads zeros); its epilogue stores the run's own rows only.  Otherwise the persistent single-CTA kernel above: the
+// same ring, the same two accumulators, the same epilogues (store, gated).
+constexpr int kMaxGroups = 256;
+
+struct GroupedArgs {
+    const int* offsets;    // [n_groups + 1]
+    int n_groups;
+};
+
+__device__ __forceinline__ void group_tile(const int* first, const int* __restrict__ offsets, int n_groups, int tile, int BN_,
+                                           int& g, int& m0, int& m_end, int& n0) {
+    int lo = 0, hi = n_groups;                       // the last group whose first tile is not beyond `tile`
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (first[mid] <= tile) lo = mid; else hi = mid;
+    }
+    g = lo;
+    const int begin = offsets[g], end = offsets[g + 1];
+    const int rows = (end - begin + BM - 1) / BM, within = tile - first[g];
+    const int tn = within / rows, tm = within - tn * rows;
+    m0 = begin + tm * BM;
+    m_end = end;
+    n0 = tn * BN_;
+}
+
+template <int BN, int STAGES, int EPI, typename TC>
+__global__ void __launch_bounds__(kGemmTcThreads, 1)
+gemm_tcgen05_grouped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                            TC* __restrict__ C, int ldc, int N, int K, GroupedArgs groups, const RopeEpilogue rope) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ int first[kMaxGroups + 1];
+    auto& sm = *reinterpret_cast<GemmSmem<BN, STAGES>*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tiles_n = (N + BN - 1) / BN;
+    const int k_iters = (K + BK - 1) / BK;
+    const CUtensorMap* no_map = nullptr;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&sm.acc_full[b], 1); mbar_init(&sm.acc_empty[b], 4); }
+        sm.abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(2 * BN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = sm.tmem_base;
+    volatile int* abort_flag = &sm.abort_flag;
+    pdl_launch_dependents();
+    pdl_wait();
+    // the runs are a predecessor's result: the table of tiles is made after the wait, the same in every CTA
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int g = 0; g < groups.n_groups; ++g) {
+            first[g] = run;
+            run += (groups.offsets[g + 1] - groups.offsets[g] + BM - 1) / BM * tiles_n;
+        }
+        first[groups.n_groups] = run;
+    }
+    __syncthreads();
+    const int n_tiles = first[groups.n_groups];
+
+    if (warp == 0 && lane == 0) {
+        // ---- producer
+        int it = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+            int g, m0, m_end, n0;
+            group_tile(first, groups.offsets, groups.n_groups, tile, BN, g, m0, m_end, n0);
+            for (int k = 0; k < k_iters; ++k, ++it) {
+                const int s = it % STAGES;
+                if (it >= STAGES && !mbar_wait(&sm.empty[s], ((it / STAGES) - 1) & 1, abort_flag)) {
+                    *abort_flag = 1; atomicCAS(&g_gemm_status, 0, (1 << 8) | s); ok = false; break;
+                }
+                mbar_expect_tx(&sm.full[s], (BM + BN) * BK * 2);
+                tma_load_2d(sm.a[s], &map_a, k * BK, m0, &sm.full[s]);
+                tma_load_2d(sm.b[s], &map_w, k * BK, g * N + n0, &sm.full[s]);
+            }
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---- MMA issuer
+        constexpr uint32_t idesc = umma_idesc_bf16(BM, BN);
+        int it = 0, local = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++local) {
+            const int buf = local & 1;
+            if (!mbar_wait(&sm.acc_empty[buf], ((local >> 1) & 1) ^ 1, abort_flag)) {
+                *abort_flag = 1; atomicCAS(&g_gemm_status, 0, (4 << 8) | buf); break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t acc = tmem + buf * BN;
+            for (int k = 0; k < k_iters; ++k, ++it) {
+                const int s = it % STAGES;
+                if (!mbar_wait(&sm.full[s], (it / STAGES) & 1, abort_flag)) {
+                    *abort_flag = 1; atomicCAS(&g_gemm_status, 0, (2 << 8) | s); ok = false; break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint64_t ad = umma_desc(sm.a[s]), bd = umma_desc(sm.b[s]);
+#pragma unroll
+                for (int kk = 0; kk < BK / 16; ++kk)
+                    umma_bf16(acc, ad + 2 * kk, bd + 2 * kk, idesc, (k | kk) != 0);
+                umma_commit(&sm.empty[s]);
+            }
+            if (ok) umma_commit(&sm.acc_full[buf]);
+        }
+    } else if (warp >= 2) {
+        // ---- epilogue
+        const int quarter = warp & 3;
+        int local = 0;
+        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++local) {
+            const int buf = local & 1;
+            int g, m0, m_end, n0;
+            group_tile(first, groups.offsets, groups.n_groups, tile, BN, g, m0, m_end, n0);
+            bool ok = mbar_wait(&sm.acc_full[buf], (local >> 1) & 1, abort_flag);
+            if (!ok && lane == 0) { *abort_flag = 1; atomicCAS(&g_gemm_status, 0, (3 << 8) | quarter); }
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            // (rows at or beyond the run's end belong to the next group: the epilogue's row limit is the run's end)
+            epilogue_tile<BN, EPI, TC>(tmem + buf * BN, quarter, lane, m0, n0, m_end, N, C, ldc, 0, no_map, nullptr, rope);
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sm.acc_empty[buf]);
+        }
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     }
     __syncthreads();
@@ -939,7 +1085,51 @@ static int launch_spans(const void* A, int lda, const void* W, int ldw, void* C,
                               ma, mw, (TC*)C, ldc, M, N, K, (kb + spans - 1) / spans);
 }
 
+template <int BN, int STAGES, int EPI, typename TC>
+static int launch_grouped(const void* A, int lda, const void* W, void* C, int ldc, int total_rows, int N, int K, int n_groups,
+                          const int* offsets, cudaStream_t stream, const RopeEpilogue& rope) {
+    CUtensorMap ma, mw;
+    if (!make_map(&ma, A, total_rows, K, lda, BM) || !make_map(&mw, W, n_groups * N, K, K, BN)) return kErrUnsupportedSize;
+    const size_t smem = ((sizeof(GemmSmem<BN, STAGES>) + 1023) & ~(size_t)1023) + 1024;
+    static bool configured = false;
+    auto kernel = gemm_tcgen05_grouped_kernel<BN, STAGES, EPI, TC>;
+    if (!configured) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return (int)cudaGetLastError();
+        configured = true;
+    }
+    // the most tiles the runs can make: every run may end in a partly filled tile
+    const long long most = ((long long)total_rows / BM + n_groups) * ((N + BN - 1) / BN);
+    const int n_sms = sm_count();
+    const dim3 grid((unsigned)(most < n_sms ? most : n_sms));
+    return launch_pdl(kernel, grid, dim3(kGemmTcThreads), smem, stream, ma, mw, (TC*)C, ldc, N, K, GroupedArgs{offsets, n_groups}, rope);
+}
+
 }  // namespace b200
+
+// One product per group over the group's run of rows (see gemm_tcgen05_grouped_kernel): A [total_rows, K] bfloat16, W
+// [n_groups, N, K] bfloat16 and dense, offsets [n_groups + 1] on the device, C [total_rows, N] float32 (epilogue 0) or
+// [total_rows, N / 2] bfloat16 (gated epilogues 2, 3, 4 with gate_limit and gate_slope).
+extern "C" int b200_gemm_tcgen05_grouped(const void* A, int lda, const void* W, void* C, int c_dtype, int ldc, int total_rows,
+                                         int N, int K, int n_groups, const int* offsets, int epilogue, float gate_limit,
+                                         float gate_slope, cudaStream_t stream) {
+    using namespace b200;
+    if (total_rows <= 0 || N <= 0 || n_groups <= 0) return 0;
+    if (n_groups > kMaxGroups || K < 8 || K % 8 != 0 || lda % 8 != 0 || (((uintptr_t)A | (uintptr_t)W) & 15)) return kErrUnsupportedSize;
+    if (offsets == nullptr) return kErrBadArgument;
+    RopeEpilogue gated = {};
+    if (epilogue >= 2 && epilogue <= 4) {
+        if ((N & 1) || c_dtype != kBF16) return kErrBadArgument;
+        gated.gate_act = epilogue - 2;
+        gated.gate_limit = gate_limit;
+        gated.gate_slope = gate_slope;
+        if (N >= 1024) return launch_grouped<256, 4, 2, __nv_bfloat16>(A, lda, W, C, ldc, total_rows, N, K, n_groups, offsets, stream, gated);
+        return launch_grouped<128, 6, 2, __nv_bfloat16>(A, lda, W, C, ldc, total_rows, N, K, n_groups, offsets, stream, gated);
+    }
+    if (epilogue != 0 || c_dtype != kF32) return kErrBadArgument;
+    if (N >= 1024) return launch_grouped<256, 4, 0, float>(A, lda, W, C, ldc, total_rows, N, K, n_groups, offsets, stream, gated);
+    return launch_grouped<128, 6, 0, float>(A, lda, W, C, ldc, total_rows, N, K, n_groups, offsets, stream, gated);
+}
 
 // Reads and clears the status word of the tensor-core GEMM (0 = every wait completed).  Synchronises.
 extern "C" int b200_gemm_tcgen05_status() {

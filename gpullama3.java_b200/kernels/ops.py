@@ -53,6 +53,8 @@ _SIGNATURES = {
                                                 c_int, c_void_p]),
     "b200_gemm_tcgen05": ("gemm_tcgen05", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                            c_int, c_int, c_int, c_int, c_float, c_float]),
+    "b200_gemm_tcgen05_grouped": ("gemm_tcgen05", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                                   c_void_p, c_int, c_float, c_float]),
     "b200_gemm_tcgen05_qkv_rope": ("gemm_tcgen05", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p,
                                                     c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                                     c_int, c_int, c_int]),
@@ -427,6 +429,35 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: in
     _check(_fn("b200_gemm_tcgen05")(pa, lda, pw, ldw, c.data_ptr(), dtype_code(c.dtype), ldc, M, N, K, epilogue,
                                     tile_width, k_spans, cta_pair, float(gate_args[0]), float(gate_args[1]), _stream()),
            "gemm_tcgen05")
+    return True
+
+
+MAX_GEMM_GROUPS = 256   # gemm_tcgen05.cu
+
+
+def gemm_tcgen05_grouped(a: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor, c: torch.Tensor,
+                         epilogue: int = EPILOGUE_STORE, gate_args: tuple[float, float] = (0.0, 0.0)) -> bool:
+    """One product per group in one launch on tcgen05 tensor cores: c[p] = a[p] @ w[g].T for the rows p = offsets[g] ..
+    offsets[g + 1] - 1 (offsets int32 [G + 1] on the device, read there).  a [P, K] and w [G, N, K] bfloat16; c [P, N]
+    float32 (store) or [P, N / 2] bfloat16 (gated epilogues).  Returns False, having done nothing, for operands it
+    does not take."""
+    P, K = a.shape
+    G, N, Kw = w.shape
+    if (a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or G > MAX_GEMM_GROUPS or K % 8 or K < 8 or a.stride(1) != 1
+            or a.stride(0) % 8 or not w.is_contiguous() or (a.data_ptr() | w.data_ptr()) & 15):
+        return False
+    gated = epilogue in GATED_EPILOGUES
+    if (gated and (c.dtype != torch.bfloat16 or N % 2)) or (not gated and (epilogue != EPILOGUE_STORE or c.dtype != torch.float32)):
+        return False
+    _dev(a, w, offsets, c)
+    assert Kw == K and offsets.dtype == torch.int32 and offsets.numel() == G + 1 and c.stride(1) == 1
+    assert tuple(c.shape) == (P, N // 2 if gated else N)
+    status = _fn("b200_gemm_tcgen05_grouped")(a.data_ptr(), a.stride(0), w.data_ptr(), c.data_ptr(), dtype_code(c.dtype),
+                                              c.stride(0), P, N, K, G, offsets.data_ptr(), epilogue, float(gate_args[0]),
+                                              float(gate_args[1]), _stream())
+    if status == _UNSUPPORTED:
+        return False
+    _check(status, "gemm_tcgen05_grouped")
     return True
 
 

@@ -8,9 +8,11 @@
 The router and the weights are 32-bit in both precisions.  The (token, choice) pairs are ordered by expert.  A step of
 few tokens then runs every expert's rows as a weight-streaming product whose row counts are read on the device, so a
 decode step's launches do not depend on the routing and can be recorded; an expert's weights are read once for all the
-tokens that chose it, and not at all when none did.  A prompt's rows are one product per expert of the same kernels the
-dense feed-forward uses (gated epilogue included); the per-expert row counts come back to the host for that, which is
-why a prompt pass of this part is not replayed from a recording."""
+tokens that chose it, and not at all when none did.  A prompt's rows are gathered into the order of their experts and
+multiplied by one launch of the tcgen05 product over all experts' tiles (gated epilogue included), which reads the runs
+on the device as well.  Only where that kernel does not take the operands (the float32 run, sizes off its grid) do
+the per-expert row counts come back to the host, for one product per expert through the kernels the dense feed-forward
+uses; that wait is why a prompt pass of this part is not replayed from a recording."""
 from __future__ import annotations
 
 import torch
@@ -24,7 +26,7 @@ from .linear import Linear
 
 class RoutedFeedForward(FeedForward):
     graph_safe = True    # (decode steps: the pair kernels read the routing from device memory)
-    pad_safe = False     # a prompt pass reads the experts' row counts on the host
+    pad_safe = False     # a prompt pass may read the experts' row counts on the host
 
     def __init__(self, hidden_size: int, intermediate_size: int, n_experts: int, top: int, groups: int = 1,
                  keep_groups: int | None = None, activation: str = "silu", limit: float | None = None, slope: float = 1.0,
@@ -74,9 +76,9 @@ class RoutedFeedForward(FeedForward):
         ops.moe_route(x, self.router, chosen, weights, self.groups, self.keep_groups, self.weight_eps, scores)
         return chosen, weights
 
-    def on_host(self, ctx: StepContext, n_tokens: int) -> bool:
-        """Whether the experts' products are launched from the host's knowledge of their row counts (prompts: dense
-        products on the tensor cores), or by kernels that read the counts on the device (steps of few tokens)."""
+    def as_prompt(self, ctx: StepContext, n_tokens: int) -> bool:
+        """Whether the experts' rows are gathered and multiplied as dense products (prompts), or streamed past the
+        experts' weights a few rows at a time (steps of few tokens)."""
         return (not ctx.all_decode) and n_tokens > 64 and n_tokens * self.top >= 16 * self.n_experts
 
     def forward(self, x, ctx: StepContext, residual, then_norm=None):
@@ -88,19 +90,23 @@ class RoutedFeedForward(FeedForward):
         ops.moe_group(chosen, self.n_experts, offsets, order, place)
         y = ctx.empty((pairs, self.intermediate_size), ctx.dtype)
         o = ctx.empty((pairs, self.hidden_size), torch.float32)
-        if not self.on_host(ctx, T):
+        if not self.as_prompt(ctx, T):
             ops.moe_rows(x, self.w_gate_up, offsets, y, order=order, top=self.top, activation=self.activation,
                          gate_args=self.gate_args)
             ops.moe_rows(y, self.w_down, offsets, o)
         else:
-            bounds = offsets.tolist()                               # (waits for the routing: the products' row counts)
             xs = ctx.empty((pairs, self.hidden_size), ctx.dtype)
             ops.moe_gather(x, order, xs, self.top)
-            for e in range(self.n_experts):
-                lo, hi = bounds[e], bounds[e + 1]
-                if hi > lo:
-                    self.gate_up[e].gated_into(xs[lo:hi], y[lo:hi], self.activation, self.gate_args)
-                    self.down[e].into(y[lo:hi], o[lo:hi])
+            # one launch over all experts' tiles, the runs read on the device; where that kernel does not take the operands
+            # (the float32 run, odd sizes) one product per expert, for which the runs' lengths come back to the host
+            if not (ops.gemm_tcgen05_grouped(xs, self.w_gate_up, offsets, y, ops.GATED_EPILOGUE_OF[self.activation], self.gate_args)
+                    and ops.gemm_tcgen05_grouped(y, self.w_down, offsets, o)):
+                bounds = offsets.tolist()
+                for e in range(self.n_experts):
+                    lo, hi = bounds[e], bounds[e + 1]
+                    if hi > lo:
+                        self.gate_up[e].gated_into(xs[lo:hi], y[lo:hi], self.activation, self.gate_args)
+                        self.down[e].into(y[lo:hi], o[lo:hi])
         ops.moe_combine(o, place, weights, residual)
         return None
 

@@ -1,6 +1,6 @@
 """Pekerax's mechanisms one at a time, each against its function of the plain implementation: the layer norm, the
-clamped gated unit in the products' epilogues, the router (scores, groups, choice, weights), the experts with their row
-counts read on the device and on the host, and one-layer models that hold nothing but an attention mixer or a delta mixer."""
+clamped gated unit in the products' epilogues, the router (scores, groups, choice, weights), the experts streamed and as
+dense products, and one-layer models that hold nothing but an attention mixer or a delta mixer."""
 import types
 
 import pytest
@@ -91,8 +91,8 @@ def test_router(experts, groups, keep, top):
 @DTYPES
 @pytest.mark.parametrize("tokens, decode", [(1, True), (7, True), (50, False), (400, False)])
 def test_routed_feed_forward(dtype, tokens, decode):
-    """Row counts read on the device (few tokens, decode steps) and on the host (prompts) against the plain mixture;
-    the two ways agree with each other far closer than the precision's tolerance."""
+    """Rows streamed past the experts' weights (few tokens, decode steps) and gathered into dense products (prompts)
+    against the plain mixture; the two ways agree with each other far closer than the precision's tolerance."""
     from gpullama3.java_b200.parts.routed_feed_forward import RoutedFeedForward
 
     g = torch.Generator().manual_seed(tokens)
@@ -106,7 +106,7 @@ def test_routed_feed_forward(dtype, tokens, decode):
     part.load(ws, dtype, torch.device("cuda"))
     ctx = types.SimpleNamespace(dtype=dtype, all_decode=decode, n_tokens=tokens,
                                 empty=lambda shape, dt: torch.empty(tuple(shape), dtype=dt, device="cuda"))
-    assert part.on_host(ctx, tokens) == (tokens == 400)
+    assert part.as_prompt(ctx, tokens) == (tokens == 400)
     residual = torch.full((tokens, width), 0.5, device="cuda")
     part.forward(x.to(dtype).cuda(), ctx, residual)
     W = {"p." + k: v.to(F) for k, v in ws.items()}
@@ -114,9 +114,9 @@ def test_routed_feed_forward(dtype, tokens, decode):
     _close(residual, ref, dtype, f"routed feed-forward, {tokens} tokens")
     if tokens == 400:   # the same step through the kernels that read the counts themselves
         other = torch.full((tokens, width), 0.5, device="cuda")
-        part.on_host = lambda ctx, n: False
+        part.as_prompt = lambda ctx, n: False
         part.forward(x.to(dtype).cuda(), ctx, other)
-        _close(other, residual, dtype, "counts on the device against counts on the host", f32=2e-6, bf16=4e-3)
+        _close(other, residual, dtype, "streamed against gathered", f32=2e-6, bf16=4e-3)
 
 
 def _one_layer(kind):

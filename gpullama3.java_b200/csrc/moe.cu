@@ -21,7 +21,6 @@
 namespace b200 {
 
 constexpr int kMaxExperts = 1024;
-constexpr int kMaxTop = 32;
 
 template <typename T> struct Piece;  // 16 bytes of storage type T as floats
 template <> struct Piece<float> {
@@ -448,14 +447,20 @@ moe_group_kernel(const int* __restrict__ chosen, int n_pairs, int n_experts, int
     }
 }
 
-// x_sorted[p] = h[order[p] / top]
+// x_sorted[p] = h[order[p] / top]; 16 bytes per thread and step when the rows allow
 template <typename T>
 __global__ void moe_gather_kernel(const T* __restrict__ h, int ld_h, const int* __restrict__ order, T* __restrict__ out,
-                                  int width, int top) {
+                                  int width, int top, int vec) {
     const int p = blockIdx.x;
     const T* src = h + (size_t)(order[p] / top) * ld_h;
     T* dst = out + (size_t)p * width;
-    for (int k = threadIdx.x; k < width; k += blockDim.x) dst[k] = src[k];
+    if (vec) {
+        const int n = width * (int)sizeof(T) / 16;
+        for (int i = threadIdx.x; i < n; i += blockDim.x)
+            reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
+    } else {
+        for (int k = threadIdx.x; k < width; k += blockDim.x) dst[k] = src[k];
+    }
 }
 
 // residual[t] += sum_k weights[t][k] o[place[t top + k]], in the order of choice
@@ -559,8 +564,10 @@ extern "C" int b200_moe_group(const int* chosen, int n_pairs, int n_experts, int
 extern "C" int b200_moe_gather(const void* h, int ld_h, int dtype, const int* order, void* out, int n_pairs, int width,
                                int top, cudaStream_t stream) {
     if (n_pairs <= 0) return 0;
+    const int el = dtype == b200::kF32 ? 4 : 2;
+    const int vec = (width * el) % 16 == 0 && (ld_h * el) % 16 == 0 && ((((uintptr_t)h) | ((uintptr_t)out)) & 15) == 0;
     B200_DISPATCH_DTYPE(dtype, T,
-        b200::moe_gather_kernel<T><<<n_pairs, 128, 0, stream>>>((const T*)h, ld_h, order, (T*)out, width, top));
+        b200::moe_gather_kernel<T><<<n_pairs, 128, 0, stream>>>((const T*)h, ld_h, order, (T*)out, width, top, vec));
     return b200::launch_status();
 }
 

@@ -62,7 +62,7 @@ def test_clamped_gated_unit(dtype, tokens, limit):
     _close(residual, ref, dtype, f"clamped unit, {tokens} rows")
 
 
-@pytest.mark.parametrize("experts, groups, keep, top", [(8, 2, 1, 2), (6, 3, 2, 2), (9, 3, 3, 4), (4, 1, 1, 1), (2, 1, 1, 2),
+@pytest.mark.parametrize("experts, groups, keep, top", [(10, 2, 1, 3), (6, 3, 2, 2), (9, 3, 3, 4), (4, 1, 1, 1), (2, 1, 1, 2),
                                                          (64, 8, 3, 6), (40, 1, 1, 8)])
 def test_router(experts, groups, keep, top):
     from gpullama3.java_b200.kernels import ops

@@ -152,14 +152,16 @@ __device__ __forceinline__ bool span_plan(const int* __restrict__ kv_lens, int n
 
 // KB: head_dim / 32.  FUSED: rotation and cache write of the step done here.  HI: the group has more than 8 heads,
 // so rows 8..15 of the tiles exist (without them a lane keeps half the sums, and more CTAs fit an SM).
-template <int KB, bool FUSED, bool HI>
+// TERMS: the further terms are compiled in (without them the kernel is the one the Llama 3 decoder has always run).
+template <int KB, bool FUSED, bool HI, bool TERMS>
 __global__ void __launch_bounds__(kAttnDecodeThreads)
 attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, __nv_bfloat16* __restrict__ out,
                         const int* __restrict__ kv_lens, const int* __restrict__ page_table, int table_stride,
                         __nv_bfloat16* __restrict__ k_pool, __nv_bfloat16* __restrict__ v_pool,
                         float* __restrict__ part_o, float* __restrict__ part_ml, int n_heads, int n_kv_heads,
-                        int window, int n_splits, RopeArgs rope, DecodeTerms terms) {
+                        int window, int n_splits, RopeArgs rope, DecodeTerms given) {
     constexpr int D = KB * 32;
+    const DecodeTerms terms = TERMS ? given : DecodeTerms{0, nullptr, nullptr, nullptr, 0};
     constexpr int NJ = D / 8;  // output tiles of 8 dims
     constexpr int SLOTS = kAttnDecodeWarps + (FUSED ? 1 : 0);  // partials merged per CTA: the warps, and the new key
     // Rows of the tiles that exist: 8 without the upper half.  (Shared memory is taken from the SM's L1, through which the
@@ -333,11 +335,11 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, _
             for (int e = 0; e < 2; ++e) {
                 const int key = base + 8 * t + 2 * i + e;
                 const bool ok = key >= key_lo && key < key_end;
-                const float dist = (float)(q_pos - key);
-                s[i][e] = ok ? s[i][e] * inv_sqrt_d - slope_lo * dist : -INFINITY;
+                const float dist = TERMS ? (float)(q_pos - key) : 0.f;
+                s[i][e] = ok ? (TERMS ? s[i][e] * inv_sqrt_d - slope_lo * dist : s[i][e] * inv_sqrt_d) : -INFINITY;
                 bm_lo = fmaxf(bm_lo, s[i][e]);
                 if (HI) {
-                    s[i][2 + e] = ok ? s[i][2 + e] * inv_sqrt_d - slope_hi * dist : -INFINITY;
+                    s[i][2 + e] = ok ? (TERMS ? s[i][2 + e] * inv_sqrt_d - slope_hi * dist : s[i][2 + e] * inv_sqrt_d) : -INFINITY;
                     bm_hi = fmaxf(bm_hi, s[i][2 + e]);
                 }
             }
@@ -614,10 +616,13 @@ static int launch_attention_decode(const void* q, int q_row_stride, void* out, c
     auto vv = (__nv_bfloat16*)v_pool;
     auto oo = (__nv_bfloat16*)out;
     int st = 0;
-#define B200_LAUNCH(KB, F) do { if (group > 8) B200_LAUNCH_H(KB, F, true); else B200_LAUNCH_H(KB, F, false); } while (0)
-#define B200_LAUNCH_H(KB, F, HI)                                                                                    \
+    const bool any_term = terms.keep_first > 0 || terms.slopes || terms.sinks || terms.gate;
+    if (any_term && fused) return kErrBadArgument;   // (the fused variant is not built with the terms)
+#define B200_LAUNCH(KB, F) do { if (group > 8) B200_LAUNCH_T(KB, F, true); else B200_LAUNCH_T(KB, F, false); } while (0)
+#define B200_LAUNCH_T(KB, F, HI) do { if (!F && any_term) B200_LAUNCH_H(KB, F, HI, !F); else B200_LAUNCH_H(KB, F, HI, false); } while (0)
+#define B200_LAUNCH_H(KB, F, HI, TM)                                                                                \
     do {                                                                                                            \
-        auto kernel = attention_decode_kernel<KB, F, HI>;                                                             \
+        auto kernel = attention_decode_kernel<KB, F, HI, TM>;                                                         \
         if (smem > 48 * 1024) {                                                                                     \
             static bool configured = false;                                                                         \
             if (!configured) {                                                                                      \
@@ -639,6 +644,7 @@ static int launch_attention_decode(const void* q, int q_row_stride, void* out, c
     }
 #undef B200_PICK
 #undef B200_LAUNCH
+#undef B200_LAUNCH_T
 #undef B200_LAUNCH_H
     if (st != 0 || n_splits == 1) return st;
     return launch_pdl(attention_decode_merge_kernel, dim3(n_seqs * n_heads), dim3(head_dim <= 64 ? 64 : 128), 0, stream,
@@ -660,7 +666,7 @@ extern "C" int b200_attention_decode_ctas_per_sm(int head_dim, int group, int fu
     cudaError_t e = cudaSuccess;
 #define B200_OCC_H(KB, F, HI)                                                                                          \
     do {                                                                                                              \
-        auto kernel = attention_decode_kernel<KB, F, HI>;                                                             \
+        auto kernel = attention_decode_kernel<KB, F, HI, false>;                                                      \
         if (smem > 48 * 1024) e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
         if (e == cudaSuccess) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, kAttnDecodeThreads, smem); \
     } while (0)

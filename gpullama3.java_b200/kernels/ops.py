@@ -969,6 +969,11 @@ def moe_route(h: torch.Tensor, router: torch.Tensor, chosen: torch.Tensor, weigh
                                  int(n_groups), int(keep_groups), chosen.shape[1], float(norm_eps), _stream()), "moe_route")
 
 
+def moe_rows_takes(k: int, dtype: torch.dtype) -> bool:
+    """Whether ``moe_rows`` can stage its eight rows of ``k`` numbers in shared memory."""
+    return 8 * (k + 8) * (4 if dtype == torch.float32 else 2) + 4096 <= 200 * 1024
+
+
 def moe_rows(a: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor, out: torch.Tensor, *, order: torch.Tensor | None = None,
              top: int = 1, activation: str | None = None, gate_args=(0.0, 0.0)) -> None:
     """One weight-streaming product per expert: out[p] = a[row(p)] @ w[e].T for the places p = offsets[e] ..

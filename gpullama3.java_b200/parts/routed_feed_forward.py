@@ -79,6 +79,8 @@ class RoutedFeedForward(FeedForward):
     def as_prompt(self, ctx: StepContext, n_tokens: int) -> bool:
         """Whether the experts' rows are gathered and multiplied as dense products (prompts), or streamed past the
         experts' weights a few rows at a time (steps of few tokens)."""
+        if not ops.moe_rows_takes(max(self.hidden_size, self.intermediate_size), ctx.dtype):
+            return True     # (rows too long to stage for the streaming kernel)
         return (not ctx.all_decode) and n_tokens > 64 and n_tokens * self.top >= 16 * self.n_experts
 
     def forward(self, x, ctx: StepContext, residual, then_norm=None):

@@ -68,6 +68,10 @@ class RoutedFeedForward(FeedForward):
             self.w_down[e] = tensors[f"e{e}.down"].to(device=device, dtype=run)
         self.gate_up = [Linear(self.w_gate_up[e]) for e in range(E)]
         self.down = [Linear(self.w_down[e]) for e in range(E)]
+        # a decode step's launches depend on device memory alone when the streaming kernel takes the rows, or else when
+        # the grouped product does (the per-expert products need the runs' lengths on the host)
+        grouped = run == torch.bfloat16 and E <= ops.MAX_GEMM_GROUPS and h % 8 == 0 and ff % 8 == 0
+        self.graph_safe = ops.moe_rows_takes(max(h, ff), run) or grouped
 
     def route(self, x: torch.Tensor, ctx: StepContext, scores: torch.Tensor | None = None):
         T = x.shape[0]

@@ -119,6 +119,33 @@ def test_routed_feed_forward(dtype, tokens, decode):
         _close(other, residual, dtype, "streamed against gathered", f32=2e-6, bf16=4e-3)
 
 
+@DTYPES
+def test_routed_feed_forward_with_rows_too_long_to_stage(dtype, monkeypatch):
+    """When the streaming kernel cannot stage the rows, a step of few tokens goes the prompts' way: the grouped product
+    in bfloat16, one product per expert in float32 (which is then no longer safe to record)."""
+    from gpullama3.java_b200.kernels import ops
+    from gpullama3.java_b200.parts.routed_feed_forward import RoutedFeedForward
+
+    monkeypatch.setattr(ops, "moe_rows_takes", lambda k, dt: False)
+    g = torch.Generator().manual_seed(5)
+    width, ff, E, top, tokens = 64, 48, 5, 3, 6
+    ws = {"router": (torch.randn(E, width, generator=g) * 0.5).to(torch.bfloat16).float()}
+    for e in range(E):
+        for n, s in (("gate", (ff, width)), ("up", (ff, width)), ("down", (width, ff))):
+            ws[f"e{e}.{n}"] = (torch.randn(s, generator=g) * 0.3).to(torch.bfloat16).float()
+    x = torch.randn(tokens, width, generator=g).to(torch.bfloat16).float()
+    part = RoutedFeedForward(width, ff, E, top, activation="clamped_sigmoid", limit=0.9, slope=1.702)
+    part.load(ws, dtype, torch.device("cuda"))
+    assert part.graph_safe == (dtype == torch.bfloat16)
+    ctx = types.SimpleNamespace(dtype=dtype, all_decode=True, n_tokens=tokens,
+                                empty=lambda shape, dt: torch.empty(tuple(shape), dtype=dt, device="cuda"))
+    assert part.as_prompt(ctx, tokens)
+    residual = torch.zeros(tokens, width, device="cuda")
+    part.forward(x.to(dtype).cuda(), ctx, residual)
+    W = {"p." + k: v.to(F) for k, v in ws.items()}
+    _close(residual, P.mixture_of_experts(x.to(F), W, "p.", E, 1, 1, top, 0.9), dtype, "rows too long to stage")
+
+
 def _one_layer(kind):
     if kind == "attention":
         layer = {"type": "attention", "mlp": None,

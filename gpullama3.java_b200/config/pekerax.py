@@ -9,7 +9,7 @@ feed-forward; every norm is a layer norm with weight and bias (``norm.eps``); th
   ``vdim``, ``conv`` taps);
   ``attention``: grouped-query attention without rotation (``heads``, ``kv_heads``, ``dim``, ``vdim``, score ``scale``),
   with a weighted RMS norm over the whole query and key projections, a distance penalty per head, a sliding window
-  ``mask.size`` behind which the first ``mask.keep_first`` positions stay visible, a learned sink per head, an output
+  ``mask.size`` behind which the first ``mask.keep_first`` positions stay visible (no ``mask``: no window), a learned sink per head, an output
   gate per head, and, where ``v_mix`` is set, values mixed with those of the first such layer;
 * ``layers[i].mlp`` is null, ``{"kind": "dense", "ff", "limit"}`` or ``{"kind": "moe", "expert": {"ff", "limit"},
   "router": {"experts", "top", "groups": {"count", "keep"}}}``; both kinds use the clamped gated unit
@@ -80,21 +80,21 @@ class PekeraxConfig(ModelConfig):
             kind, m = L.get("type"), dict(L["mixer"])
             if kind not in MIXER_TYPES:
                 raise ConfigError(f"{where}: unknown mixer type {kind!r}; known: {', '.join(MIXER_TYPES)}")
-            need = {"attention": ["heads", "kv_heads", "dim", "vdim", "scale", "mask"],
+            need = {"attention": ["heads", "kv_heads", "dim", "vdim", "scale"],
                     "delta": ["heads", "kv_heads", "dim", "vdim", "conv"]}[kind]
             require_keys(m, need, where)
             for key in need:
                 if key == "scale":
                     _positive(m, key, where)
-                elif key == "mask":
-                    if not isinstance(m["mask"], dict):
-                        raise ConfigError(f"{where}: mask must be an object with 'size' (and 'keep_first')")
-                    require_keys(m["mask"], ["size"], where + " mask")
-                    as_int(m["mask"], "size")
-                    if m["mask"].get("keep_first") is not None:
-                        as_int(m["mask"], "keep_first", minimum=0)
                 else:
                     as_int(m, key)
+            if kind == "attention" and m.get("mask") is not None:      # (no mask: every earlier position is visible)
+                if not isinstance(m["mask"], dict):
+                    raise ConfigError(f"{where}: mask must be an object with 'size' (and 'keep_first')")
+                require_keys(m["mask"], ["size"], where + " mask")
+                as_int(m["mask"], "size")
+                if m["mask"].get("keep_first") is not None:
+                    as_int(m["mask"], "keep_first", minimum=0)
             if m["heads"] % m["kv_heads"]:
                 raise ConfigError(f"{where}: heads {m['heads']} is not a multiple of kv_heads {m['kv_heads']}")
             mlp = L.get("mlp")
@@ -165,8 +165,9 @@ class PekeraxConfig(ModelConfig):
         if L.type == "attention":
             return PartSpec("mixer", "attention", {
                 "hidden_size": h, "n_heads": m["heads"], "n_kv_heads": m["kv_heads"], "head_dim": m["dim"],
-                "value_dim": m["vdim"], "position": PartSpec("position", "none", {}), "window": m["mask"]["size"],
-                "keep_first": int(m["mask"].get("keep_first") or 0), "qk_norm_eps": self.norm_eps, "projection_norm": True,
+                "value_dim": m["vdim"], "position": PartSpec("position", "none", {}),
+                "window": (m.get("mask") or {}).get("size"), "keep_first": int((m.get("mask") or {}).get("keep_first") or 0),
+                "qk_norm_eps": self.norm_eps, "projection_norm": True,
                 "scale": float(m["scale"]), "distance_slope_base": DISTANCE_SLOPE_BASE, "sink": True,
                 "value_mix": self._value_mix(i), "output_gate": True})
         return PartSpec("mixer", "head_delta", {

@@ -108,7 +108,8 @@ def attention_mixer(h, W, p, m, eps, v_first):
     if v_first is not None:
         lam = W[p + "vmix"]
         v = (1.0 - lam) * v + lam * v_first
-    mask = kept_window_mask(T, m["mask"]["size"], m["mask"].get("keep_first", 0))
+    rule = m.get("mask") or {"size": T}       # (no mask: every earlier position is visible)
+    mask = kept_window_mask(T, rule["size"], rule.get("keep_first") or 0)
     o = sink_attention(q.view(T, H, d), k.view(T, G, d), v.view(T, G, dv), m["scale"], mask, head_slopes(H), W[p + "sink"])
     o = o * torch.sigmoid(h @ W[p + "g"].T)[:, :, None]
     return o.reshape(T, H * dv) @ W[p + "o"].T, own_v

@@ -150,6 +150,9 @@ def _one_layer(kind):
     if kind == "attention of 12 heads on one, 96 wide":   # the decode kernel's upper tile rows, the flash kernel's third size
         layer = {"type": "attention", "mlp": None,
                  "mixer": {"heads": 12, "kv_heads": 1, "dim": 80, "vdim": 96, "scale": 0.3, "mask": {"size": 37, "keep_first": 33}}}
+    elif kind == "attention without a mask":
+        layer = {"type": "attention", "mlp": None,
+                 "mixer": {"heads": 2, "kv_heads": 2, "dim": 32, "vdim": 16, "scale": 0.4}}
     elif kind == "attention":
         layer = {"type": "attention", "mlp": None,
                  "mixer": {"heads": 4, "kv_heads": 2, "dim": 16, "vdim": 24, "scale": 0.5, "mask": {"size": 50, "keep_first": 2},
@@ -161,7 +164,7 @@ def _one_layer(kind):
 
 
 @DTYPES
-@pytest.mark.parametrize("kind", ["attention", "attention of 12 heads on one, 96 wide", "delta"])
+@pytest.mark.parametrize("kind", ["attention", "attention of 12 heads on one, 96 wide", "attention without a mask", "delta"])
 def test_one_mixer_alone(session_tmp, dtype, kind):
     from gpullama3.java_b200.engine.step import SequenceInput, StepFunction
     from gpullama3.java_b200.engine.trace import load_model

@@ -26,6 +26,13 @@ def test_round_trip_and_parts(name):
     assert cfg.embedding_scale() == CONFIGS[name].get("embedding", {}).get("scale", 1.0)
 
 
+def test_no_mask_means_no_window():
+    d = copy.deepcopy(PEKERAX_A)
+    del d["layers"][2]["mixer"]["mask"]
+    args = config_from_dict(d).layer_specs()[2].parts["mixer"].args
+    assert args["window"] is None and args["keep_first"] == 0
+
+
 def test_value_mixing_roles():
     cfg = config_from_dict(PEKERAX_A)
     roles = [s.parts["mixer"].args.get("value_mix") for s in cfg.layer_specs()]
@@ -50,7 +57,7 @@ def test_checkpoint_names_and_shapes():
 
 @pytest.mark.parametrize("change, message", [
     (lambda d: d["layers"][0].update(type="recurrent"), "unknown mixer type"),
-    (lambda d: d["layers"][0]["mixer"].pop("mask"), "missing key"),
+    (lambda d: d["layers"][0]["mixer"]["mask"].pop("size"), "missing key"),
     (lambda d: d["layers"][0]["mixer"].update(kv_heads=3), "multiple"),
     (lambda d: d["layers"][1]["mlp"]["router"].update(top=5), "experts"),
     (lambda d: d["layers"][1]["mlp"]["router"]["groups"].update(count=4), "groups"),
